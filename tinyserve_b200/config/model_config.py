@@ -53,6 +53,8 @@ class LayerSpec:
     norm: PartSpec
     arrangement: str = "pre_norm"
     names: dict = field(default_factory=dict)
+    # what else the arrangement wants to know (post_norm: "input_conv_taps")
+    options: dict = field(default_factory=dict)
 
     def name_of(self, key: str, default: str = "") -> str:
         return self.names.get(key, LAYER_NAMES.get(key, default))

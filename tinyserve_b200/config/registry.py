@@ -14,6 +14,7 @@ import os
 from .delilorn import DelilornConfig
 from .dudatar import DudatarConfig
 from .model_config import ConfigError, ModelConfig, Qwen3Config
+from .tarivik import TarivikConfig
 
 ARCHITECTURES: dict[str, type] = {}
 
@@ -62,3 +63,4 @@ def load_model_config(model_dir: str) -> ModelConfig:
 register_architecture(Qwen3Config.architecture, Qwen3Config)
 register_architecture(DudatarConfig.architecture, DudatarConfig)
 register_architecture(DelilornConfig.architecture, DelilornConfig)
+register_architecture(TarivikConfig.architecture, TarivikConfig)

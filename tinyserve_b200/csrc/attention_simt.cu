@@ -48,6 +48,8 @@ struct AttnParams {
   int num_splits, window;
   int keep_first;           // with a window: keys below this stay visible
   const float* sinks;       // [H] or null: one more term exp(sinks[h]) in every softmax sum of head h
+  int chunk;                // > 0: a query at position i sees key j only if i / chunk == j / chunk (no window then)
+  const float* slopes;      // [H] or null: slopes[h] * (i - j) is taken off the score of head h
   float scale;
 };
 
@@ -111,7 +113,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(AttnParams 
 
   // key range of this tile and of this split
   const int j_hi = min(kv_len, pos0 + nq);
-  const int j_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int j_lo = p.chunk > 0 ? pos0 / p.chunk * p.chunk : (p.window > 0 ? max(0, pos0 - p.window + 1) : 0);
   const int first_tile = j_lo / BN;
   // the tiles of the kept first keys that lie before the window's first tile come first in the walk
   const int keep = p.window > 0 ? min(p.keep_first, j_hi) : 0;
@@ -170,7 +172,9 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(AttnParams 
       for (int d = 0; d < D; ++d) s = fmaf(qr[d], kr[d], s);
       s *= p.scale;
       const int pos = pos0 + (p.queries_per_tile > 1 ? r / GT : 0);
-      const bool visible = j <= pos && j < j_hi && (p.window <= 0 || j > pos - p.window || j < keep);
+      const bool visible = j <= pos && j < j_hi && (p.window <= 0 || j > pos - p.window || j < keep) &&
+                           (p.chunk <= 0 || j >= pos / p.chunk * p.chunk);
+      if (p.slopes) s -= p.slopes[kvh * G + g0 + (p.queries_per_tile > 1 ? r % GT : r)] * (float)(pos - j);
       s = visible ? s : -INFINITY;
       const float m_new = fmaxf(m[i], warp_max(s));
       const float prob = (s == -INFINITY) ? 0.f : expf(s - m_new);
@@ -267,13 +271,17 @@ size_t smem_bytes() { return sizeof(float) * (BM * D + BN * KS + BN * D + BM * B
 TS_EXPORT int ts_attention_head_dim() { return D; }
 
 // Scratch for num_splits > 1: part_o holds T*H*splits*D floats, part_ml T*H*splits*2.
-TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void* k_cache,
-                                 const void* v_cache, const int* block_table, const int* cu_q,
-                                 const int* kv_lens, int num_tokens, int num_requests,
-                                 int max_q_len, int H, int Hkv, int page_size, int max_blocks,
-                                 float scale, int window, int num_splits, float* part_o,
-                                 float* part_ml, int keep_first, const float* sinks, cudaStream_t stream) {
+// `chunk` > 0: queries see the keys of their own chunk of that many positions only (counted from
+// position 0; no window then).  `slopes` [H]: slopes[h] * (i - j) is taken off head h's scores.
+TS_EXPORT int ts_paged_attention_biased(int dtype, const void* q, void* out, const void* k_cache,
+                                        const void* v_cache, const int* block_table, const int* cu_q,
+                                        const int* kv_lens, int num_tokens, int num_requests,
+                                        int max_q_len, int H, int Hkv, int page_size, int max_blocks,
+                                        float scale, int window, int num_splits, float* part_o,
+                                        float* part_ml, int keep_first, const float* sinks, int chunk,
+                                        const float* slopes, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention: empty batch");
+  TS_REQUIRE(chunk >= 0 && (chunk == 0 || window <= 0), "paged_attention: a chunk of %d positions (and no window beside it)", chunk);
   TS_REQUIRE(keep_first >= 0, "paged_attention: keep_first %d", keep_first);
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size > 0 && max_blocks > 0, "paged_attention: bad page geometry");
@@ -291,6 +299,7 @@ TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void
   p.head_tiles = (G + p.heads_per_tile - 1) / p.heads_per_tile;
   p.num_splits = num_splits; p.window = window; p.scale = scale;
   p.keep_first = keep_first; p.sinks = sinks;
+  p.chunk = chunk; p.slopes = slopes;
   const long long gz = (long long)num_requests * num_splits;
   const long long gy = (long long)Hkv * p.head_tiles;
   TS_REQUIRE(gz <= 65535 && gy <= 65535, "paged_attention: grid too large (%lld requests*splits, %lld head tiles)", gz, gy);
@@ -314,6 +323,17 @@ TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void
       TS_LAUNCH("attention_combine", attention_combine_kernel<__nv_bfloat16>, num_tokens * H, threads, 0, stream, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, num_splits, sinks, H);
   }
   return 0;
+}
+
+TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void* k_cache,
+                                 const void* v_cache, const int* block_table, const int* cu_q,
+                                 const int* kv_lens, int num_tokens, int num_requests,
+                                 int max_q_len, int H, int Hkv, int page_size, int max_blocks,
+                                 float scale, int window, int num_splits, float* part_o,
+                                 float* part_ml, int keep_first, const float* sinks, cudaStream_t stream) {
+  return ts_paged_attention_biased(dtype, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens, num_requests,
+                                   max_q_len, H, Hkv, page_size, max_blocks, scale, window, num_splits, part_o, part_ml,
+                                   keep_first, sinks, 0, nullptr, stream);
 }
 
 // ------------------------------------------------------------------ no-allocation entry point

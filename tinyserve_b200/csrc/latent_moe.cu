@@ -13,6 +13,10 @@
 //  * ts_moe_route: softmax over all experts of a token's router logits; the `top` largest keep
 //    their probability (not renormalised), the others get zero.
 //  * ts_moe_activate: a[t, e, :] <- act(a[t, e, :]) * gate[t, e], act = relu squared.
+//  * ts_moe_route_scored: scores s = sigmoid(z); the choice is made on s + correction, among the
+//    experts of the `keep` best of `groups` equal groups of neighbours (a group's score: the sum of
+//    its two largest choice scores); the `top` chosen experts keep s as their weight.
+//  * ts_moe_gated_activate: out[t, e, :] = silu(a[t, e, :ff]) * a[t, e, ff:] * gate[t, e].
 //  * ts_moe_group, ts_moe_gather, ts_moe_combine: the tokens of a step sorted by expert (every
 //    expert's rows a run that starts at a multiple of 16), their inputs gathered into that order,
 //    and the experts' outputs added back per token with the router's weights in 32-bit.
@@ -176,6 +180,108 @@ __device__ __forceinline__ void route_token(const float* __restrict__ z, float* 
   }
   for (int e = lane; e < E; e += 32)
     if (g[e] < 0.f) g[e] = 0.f;
+}
+
+// One warp, one token.  z [E] logits, corr [E] or null -> g [E]: sigmoid(z) for the chosen experts,
+// zero for the others.  scratch: 2 E + 2 groups floats of this warp's own.  Ties go to the lower number.
+__device__ __forceinline__ void warp_argmax(float& best, int& at) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+    if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+  }
+}
+__device__ __forceinline__ void route_token_scored(const float* __restrict__ z, const float* __restrict__ corr, float* g,
+                                                   float* scratch, int E, int top, int groups, int keep, int lane) {
+  float* choice = scratch;            // [E] choice scores; minus infinity once taken or shut out
+  float* taken = scratch + E;         // [E] 1 for a chosen expert
+  float* gscore = taken + E;          // [groups]
+  float* gopen = gscore + groups;     // [groups] 1 for a group whose experts may be chosen
+  for (int e = lane; e < E; e += 32) {
+    const float s = 1.f / (1.f + expf(-z[e]));
+    g[e] = s;
+    choice[e] = s + (corr ? corr[e] : 0.f);
+    taken[e] = 0.f;
+  }
+  __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int per = E / groups;
+    for (int grp = 0; grp < groups; ++grp) {
+      float b1 = -INFINITY; int a1 = E;
+      for (int e = lane; e < per; e += 32) {
+        const float v = choice[grp * per + e];
+        if (v > b1) { b1 = v; a1 = e; }
+      }
+      warp_argmax(b1, a1);
+      float b2 = -INFINITY; int a2 = E;
+      for (int e = lane; e < per; e += 32) {
+        const float v = choice[grp * per + e];
+        if (e != a1 && v > b2) { b2 = v; a2 = e; }
+      }
+      warp_argmax(b2, a2);
+      if (lane == 0) {
+        gscore[grp] = per > 1 ? b1 + b2 : b1;
+        gopen[grp] = 0.f;
+      }
+    }
+    __syncwarp();
+    for (int k = 0; k < keep; ++k) {
+      float best = -INFINITY; int at = groups;
+      for (int grp = lane; grp < groups; grp += 32)
+        if (gopen[grp] == 0.f && (gscore[grp] > best || at == groups)) { best = gscore[grp]; at = grp; }
+      // (a group of score minus infinity is still a group: `at` starts at the first open one)
+      warp_argmax(best, at);
+      if (lane == 0 && at < groups) gopen[at] = 1.f;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (gopen[e / per] == 0.f) choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY; int at = E;
+    for (int e = lane; e < E; e += 32)
+      if (choice[e] > best) { best = choice[e]; at = e; }
+    warp_argmax(best, at);
+    if (lane == 0 && at < E) { taken[at] = 1.f; choice[at] = -INFINITY; }
+    __syncwarp();
+  }
+  for (int e = lane; e < E; e += 32)
+    if (taken[e] == 0.f) g[e] = 0.f;
+}
+
+__global__ void moe_route_scored_kernel(const float* __restrict__ logits, const float* __restrict__ corr,
+                                        float* __restrict__ gates, int num_tokens, int E, int top, int groups, int keep) {
+  extern __shared__ float route_scratch[];
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= num_tokens) return;
+  route_token_scored(logits + (size_t)t * E, corr, gates + (size_t)t * E, route_scratch + (size_t)warp * (2 * E + 2 * groups), E,
+                     top, groups, keep, lane);
+}
+
+// out[r, e * ff + j] = silu(a[r, e * 2 ff + j]) * a[r, e * 2 ff + ff + j] * gates[r, e] (gates null: 1)
+template <typename T>
+__global__ void moe_gated_activate_kernel(const T* __restrict__ a, const float* __restrict__ gates, int E, int ff,
+                                          T* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t r = blockIdx.x;
+  const T* row = a + r * (size_t)E * 2 * ff;
+  T* dst = out + r * (size_t)E * ff;
+  for (int i = threadIdx.x; i < E * ff; i += blockDim.x) {
+    const int e = i / ff, j = i % ff;
+    const float g = gates ? gates[r * E + e] : 1.f;
+    float y = 0.f;
+    if (g != 0.f) {
+      const float gate = to_f32<T>(row[(size_t)e * 2 * ff + j]), up = to_f32<T>(row[(size_t)e * 2 * ff + ff + j]);
+      y = gate / (1.f + expf(-gate)) * up * g;
+    }
+    dst[i] = from_f32<T>(y);
+  }
 }
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, float* __restrict__ gates, int num_tokens, int E, int top) {
@@ -468,6 +574,31 @@ TS_EXPORT int ts_gate_heads(int dtype, const void* x, const void* gate, long lon
 TS_EXPORT int ts_moe_route(const float* logits, float* gates, int num_tokens, int E, int top, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && E > 0 && top > 0 && top <= E && logits && gates, "moe_route: %d of %d experts", top, E);
   TS_LAUNCH("moe_route", moe_route_kernel, (num_tokens + 3) / 4, 128, 0, stream, logits, gates, num_tokens, E, top);
+  return 0;
+}
+
+TS_EXPORT int ts_moe_route_scored(const float* logits, const float* correction, float* gates, int num_tokens, int E, int top,
+                                  int groups, int keep, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && E > 0 && top > 0 && top <= E && logits && gates, "moe_route_scored: %d of %d experts", top, E);
+  TS_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups && top <= keep * (E / groups),
+             "moe_route_scored: %d experts in %d groups, %d kept, %d chosen", E, groups, keep, top);
+  const int warps = 4;
+  const size_t smem = (size_t)warps * (2 * E + 2 * groups) * sizeof(float);
+  TS_REQUIRE(smem <= 48 * 1024, "moe_route_scored: %d experts are too many", E);
+  TS_LAUNCH("moe_route_scored", moe_route_scored_kernel, (num_tokens + warps - 1) / warps, warps * 32, smem, stream, logits,
+            correction, gates, num_tokens, E, top, groups, keep);
+  return 0;
+}
+
+TS_EXPORT int ts_moe_gated_activate(int dtype, const void* a, const float* gates, int rows, int E, int ff, void* out,
+                                    cudaStream_t stream) {
+  TS_REQUIRE(rows > 0 && E > 0 && ff > 0 && a && out, "moe_gated_activate: empty input");
+  if (dtype == TS_F32)
+    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<float>, rows, 256, 0, stream, (const float*)a, gates, E, ff, (float*)out);
+  else if (dtype == TS_BF16)
+    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<__nv_bfloat16>, rows, 256, 0, stream, (const __nv_bfloat16*)a, gates, E, ff,
+              (__nv_bfloat16*)out);
+  else return ts_fail("moe_gated_activate: unknown dtype %d", dtype);
   return 0;
 }
 

@@ -3,8 +3,14 @@
 //   S_t = diag(a_t) S_(t-1) + k_t v_t^T        (S: key size x value size, per request and head)
 //   o_t = S_t^T q_t
 //
-// a_t is either one constant per head (retention: `decay`) or one number per key channel and
-// token, a_t = sigmoid(z_t)^(1 / tau) (gated linear attention: `z` holds the 32-bit logits).
+// a_t is one constant per head (retention: `decay`), or one number per key channel and token made
+// from 32-bit logits z (gated linear attention: a_t = sigmoid(z_t)^(1 / tau); with a lower bound l per
+// channel a_t = l + (1 - l) sigmoid(z_t), and then k_t may be tied to it, k_t = 1 - a_t), or one
+// number per head and token that the caller made (`tok_keep`, with a factor `tok_write` on k_t:
+// S_t = keep_t S_(t-1) + write_t k_t v_t^T, the form of selective state spaces and of matrix
+// memories with an exponential input gate).  Several heads may share one q and k (`qk_group`).
+// The values may get constant columns behind the ones the caller brings (`v_width` < value size: a
+// column of ones, then zeros), so that S^T q also holds sum_t (...) k_t . q, a normaliser.
 // q and k may get rotary positions on their first rotary_dim elements and a constant factor
 // each.  The head's output is divided by its root mean square over the value size (times an
 // optional weight), multiplied by silu(gate) and stored as T for the output projection.
@@ -69,7 +75,7 @@ struct ScanParams {
   const void* q; const void* k; const void* v; const void* gate;
   long long ldq, ldk, ldv, ldg;           // row strides in elements
   const float* z; long long ldz;          // per-channel decay logits [T, H * DIM], or null
-  const float* decay;                     // [H], used when z is null
+  const float* decay;                     // [H], used when z and tok_keep are null
   float inv_tau;
   const int* positions; const float* cos; const float* sin; int rotary_dim;
   float q_scale, k_scale;
@@ -84,10 +90,20 @@ struct ScanParams {
   int max_segments;
   int cols, col_tiles;                    // value columns per block (a multiple of COLS); blocks per head
   float* raw_out;                         // [T, H * vdim] 32-bit o_t before norm and gate (col_tiles > 1 or joint_norm), else null
-  int in_act;                             // 1: q, k and v pass through silu as they are staged
+  int in_act;                             // bits ACT_Q, ACT_K, ACT_V: that operand passes through silu as it is staged
   int gate_act;                           // 0: the output is multiplied by silu(gate), 1: by sigmoid(gate)
   int joint_norm;                         // 1: the output norm runs over all heads of a token together (weight [H * vdim])
+  const float* lower;                     // [H * DIM] or null: a = lower + (1 - lower) sigmoid(z)
+  int tied_key;                           // 1: k = 1 - a (per-channel decays only; `k` is not read)
+  const float* tok_keep;                  // [T, H] or null: the decay of (token, head)
+  const float* tok_write;                 // [T, H]: factor on k of (token, head)
+  int qk_group;                           // heads that share one q and one k (1: every head its own)
+  int v_width;                            // value columns the caller brings per head; behind them a column of ones, then zeros
+  int finish;                             // 0: the 32-bit outputs in raw_out are all the caller wants
 };
+
+enum { DECAY_HEAD = 0, DECAY_CHANNEL = 1, DECAY_TOKEN = 2 };
+enum { ACT_Q = 1, ACT_K = 2, ACT_V = 4 };
 
 __device__ __forceinline__ float staged(float x, int in_act) { return in_act ? x / (1.f + expf(-x)) : x; }
 __device__ __forceinline__ float gate_factor(float g, int gate_act) {
@@ -117,9 +133,11 @@ __device__ __forceinline__ void prefetch_rows(const void* first, long long strid
 // from shared memory for 3 R x 4 multiply-adds, so the arithmetic, not shared memory, is what
 // it waits for.  The row groups of a column quad are neighbouring lanes and add their shares of
 // o_t by shuffles.
-template <typename T, bool PER_CHANNEL, int MODE>
+template <typename T, int DECAY, int MODE>
 __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_scan_kernel(ScanParams p) {
+  constexpr bool PER_CHANNEL = DECAY == DECAY_CHANNEL;
   extern __shared__ float smem[];
+  __shared__ float s_keep[CHUNK];                     // DECAY_TOKEN: the staged tokens' decays
   const int vdim = p.vdim, cols = p.cols;
   float* sq = smem;                                   // [CHUNK][GROUPS][RP]
   float* sk = sq + CHUNK * GROUPS * RP;
@@ -164,10 +182,13 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
       for (int j = 0; j < COLS; ++j) s[r][j] = from && owns[j] ? from[(size_t)r * vdim + j] : 0.f;
     }
   }
-  const float head_decay = PER_CHANNEL ? 1.f : p.decay[h];
-  const T* q = static_cast<const T*>(p.q) + (size_t)h * DIM;
-  const T* k = static_cast<const T*>(p.k) + (size_t)h * DIM;
-  const T* v = static_cast<const T*>(p.v) + (size_t)h * vdim;
+  const float head_decay = DECAY == DECAY_HEAD ? p.decay[h] : 1.f;
+  const int hq = h / p.qk_group, vw = p.v_width;
+  const bool tied = PER_CHANNEL && p.tied_key;
+  const int act_q = p.in_act & ACT_Q, act_k = p.in_act & ACT_K, act_v = p.in_act & ACT_V;
+  const T* q = static_cast<const T*>(p.q) + (size_t)hq * DIM;
+  const T* k = static_cast<const T*>(p.k) + (size_t)hq * DIM;
+  const T* v = static_cast<const T*>(p.v) + (size_t)h * vw;
   const T* gate = static_cast<const T*>(p.gate) + (size_t)h * vdim;
   T* out = static_cast<T*>(p.out) + (size_t)h * vdim;
   const int rot = p.rotary_dim, half = rot >> 1;
@@ -191,16 +212,21 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
       const size_t t = base + tok;
       const T* kt = k + t * p.ldk;
       const T* qt = q + t * p.ldq;
+      float k_factor = p.k_scale;
+      if (DECAY == DECAY_TOKEN) {
+        k_factor *= __ldg(p.tok_write + t * p.H + h);
+        if (lane == 0) s_keep[tok] = __ldg(p.tok_keep + t * p.H + h);
+      }
       if (half > 0) {
         const size_t at = (size_t)__ldg(p.positions + t) * half;
 #pragma unroll 2
         for (int j = lane; j < half; j += 32) {                    // a pair (j, j + half) per turn
           const float cs = __ldg(p.cos + at + j), sn = __ldg(p.sin + at + j);
-          const float ka = staged(to_f32<T>(__ldg(kt + j)), p.in_act), kb = staged(to_f32<T>(__ldg(kt + j + half)), p.in_act);
-          sk[where(tok, j)] = (ka * cs - kb * sn) * p.k_scale;
-          sk[where(tok, j + half)] = (kb * cs + ka * sn) * p.k_scale;
+          const float ka = staged(to_f32<T>(__ldg(kt + j)), act_k), kb = staged(to_f32<T>(__ldg(kt + j + half)), act_k);
+          sk[where(tok, j)] = (ka * cs - kb * sn) * k_factor;
+          sk[where(tok, j + half)] = (kb * cs + ka * sn) * k_factor;
           if (MODE != SCAN_LOCAL) {
-            const float qa = staged(to_f32<T>(__ldg(qt + j)), p.in_act), qb = staged(to_f32<T>(__ldg(qt + j + half)), p.in_act);
+            const float qa = staged(to_f32<T>(__ldg(qt + j)), act_q), qb = staged(to_f32<T>(__ldg(qt + j + half)), act_q);
             sq[where(tok, j)] = (qa * cs - qb * sn) * p.q_scale;
             sq[where(tok, j + half)] = (qb * cs + qa * sn) * p.q_scale;
           }
@@ -208,24 +234,39 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
       }
 #pragma unroll 2
       for (int i = rot + lane; i < DIM; i += 32) {                 // the elements behind the rotary ones
-        sk[where(tok, i)] = staged(to_f32<T>(__ldg(kt + i)), p.in_act) * p.k_scale;
-        if (MODE != SCAN_LOCAL) sq[where(tok, i)] = staged(to_f32<T>(__ldg(qt + i)), p.in_act) * p.q_scale;
+        if (!tied) sk[where(tok, i)] = staged(to_f32<T>(__ldg(kt + i)), act_k) * k_factor;
+        if (MODE != SCAN_LOCAL) sq[where(tok, i)] = staged(to_f32<T>(__ldg(qt + i)), act_q) * p.q_scale;
       }
       if (PER_CHANNEL) {
         const float* zt = p.z + t * p.ldz + (size_t)h * DIM;
+        const float* low = p.lower ? p.lower + (size_t)h * DIM : nullptr;
 #pragma unroll 2
-        for (int i = lane; i < DIM; i += 32) sa[where(tok, i)] = expf(log_sigmoid(__ldg(zt + i)) * p.inv_tau);
+        for (int i = lane; i < DIM; i += 32) {
+          float a, rest;      // rest = 1 - a, made without the cancellation of that difference
+          if (low) {
+            const float l = __ldg(low + i), zz = __ldg(zt + i);
+            a = l + (1.f - l) / (1.f + expf(-zz));
+            rest = (1.f - l) / (1.f + expf(zz));
+          } else {
+            a = expf(log_sigmoid(__ldg(zt + i)) * p.inv_tau);
+            rest = 1.f - a;
+          }
+          sa[where(tok, i)] = a;
+          if (tied) sk[where(tok, i)] = rest * k_factor;
+        }
       }
       const T* vt = v + t * p.ldv + col0;
 #pragma unroll 4
-      for (int i = lane; i < cols; i += 32) sv[tok * cols + i] = col0 + i < vdim ? staged(to_f32<T>(__ldg(vt + i)), p.in_act) : 0.f;
+      for (int i = lane; i < cols; i += 32)
+        sv[tok * cols + i] = col0 + i < vw ? staged(to_f32<T>(__ldg(vt + i)), act_v) : (col0 + i == vw && vw < vdim ? 1.f : 0.f);
     }
     __syncthreads();
     if (turn + 1 < chunks) {        // the next chunk's operands, on their way while this one is computed
       const int m = min(CHUNK, t1 - next);
       const size_t t = next;
-      prefetch_rows(k + t * p.ldk, p.ldk * (long long)sizeof(T), DIM * (int)sizeof(T), m, warp, warps, lane);
-      prefetch_rows(v + t * p.ldv + col0, p.ldv * (long long)sizeof(T), min(cols, vdim - col0) * (int)sizeof(T), m, warp, warps, lane);
+      if (!tied) prefetch_rows(k + t * p.ldk, p.ldk * (long long)sizeof(T), DIM * (int)sizeof(T), m, warp, warps, lane);
+      if (col0 < vw)
+        prefetch_rows(v + t * p.ldv + col0, p.ldv * (long long)sizeof(T), min(cols, vw - col0) * (int)sizeof(T), m, warp, warps, lane);
       if (PER_CHANNEL) prefetch_rows(p.z + t * p.ldz + (size_t)h * DIM, p.ldz * 4, DIM * 4, m, warp, warps, lane);
       if (MODE != SCAN_LOCAL) {
         prefetch_rows(q + t * p.ldq, p.ldq * (long long)sizeof(T), DIM * (int)sizeof(T), m, warp, warps, lane);
@@ -252,7 +293,7 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
             for (int j = 0; j < COLS; ++j) s[r][j] = fmaf(kw, vv[j], s[r][j]);
             if (PER_CHANNEL) w[r] *= ar[r];
           }
-          if (!PER_CHANNEL) w[0] *= head_decay;
+          if (!PER_CHANNEL) w[0] *= DECAY == DECAY_TOKEN ? s_keep[tok] : head_decay;
         }
       } else
       for (int tok = 0; tok < n; ++tok) {
@@ -262,9 +303,10 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
         const float4 v4 = *reinterpret_cast<const float4*>(sv + tok * cols + lc * COLS);
         const float vv[COLS] = {v4.x, v4.y, v4.z, v4.w};
         float acc[COLS] = {0.f, 0.f, 0.f, 0.f};
+        const float token_decay = DECAY == DECAY_TOKEN ? s_keep[tok] : head_decay;
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-          const float a = PER_CHANNEL ? ar[r] : head_decay;
+          const float a = PER_CHANNEL ? ar[r] : token_decay;
           const float kk = kr[r], qq = qr[r];
 #pragma unroll
           for (int j = 0; j < COLS; ++j) {
@@ -317,7 +359,7 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
       }
     }
   }
-  if (PER_CHANNEL && MODE == SCAN_LOCAL && c == 0 && in_block) {
+  if (DECAY != DECAY_HEAD && MODE == SCAN_LOCAL && c == 0 && in_block) {     // (per token: the same product for every row)
 #pragma unroll
     for (int r = 0; r < R; ++r) p.seg_decay[seg_index * DIM + g * R + r] = w[PER_CHANNEL && MODE == SCAN_LOCAL ? r : 0];
   }
@@ -368,8 +410,9 @@ __global__ void linear_attention_finish_kernel(ScanParams p, int num_tokens) {
 // segments in order.  Segment 0 starts from the request's stored state (zero for a request that
 // starts); S_(p+1) = D_p S_p + L_p with D_p the product of segment p's decays (per head: the
 // decay multiplied seg_len times, as the scan itself does).
-template <bool PER_CHANNEL>
+template <int DECAY>
 __global__ void linear_attention_combine_kernel(ScanParams p) {
+  constexpr bool PER_CHANNEL = DECAY != DECAY_HEAD;     // a stored product per (segment, row)
   pdl_trigger();
   pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y;
@@ -404,34 +447,35 @@ __global__ void linear_attention_combine_kernel(ScanParams p) {
   }
 }
 
-template <typename T, bool PER_CHANNEL, int MODE>
+template <typename T, int DECAY, int MODE>
 int launch_scan_mode(const ScanParams& p, int num_requests, int segments, cudaStream_t stream) {
   const int threads = p.cols / COLS * GROUPS;       // a multiple of 32: see the choice of cols
+  constexpr bool PER_CHANNEL = DECAY == DECAY_CHANNEL;
   const size_t smem = ((size_t)(PER_CHANNEL ? 3 : 2) * CHUNK * GROUPS * RP + 2 * (size_t)CHUNK * p.cols) * sizeof(float);
   static size_t allowed = 48 * 1024;
   if (smem > allowed) {
-    cudaError_t e = cudaFuncSetAttribute(linear_attention_scan_kernel<T, PER_CHANNEL, MODE>,
+    cudaError_t e = cudaFuncSetAttribute(linear_attention_scan_kernel<T, DECAY, MODE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return ts_fail("linear_attention: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     allowed = smem;
   }
-  TS_LAUNCH("linear_attention", (linear_attention_scan_kernel<T, PER_CHANNEL, MODE>),
+  TS_LAUNCH("linear_attention", (linear_attention_scan_kernel<T, DECAY, MODE>),
             dim3(num_requests * p.col_tiles, p.H, segments), threads, smem, stream, p);
   return 0;
 }
 
-template <typename T, bool PER_CHANNEL>
+template <typename T, int DECAY>
 int launch_scan(const ScanParams& p, int num_requests, int num_tokens, cudaStream_t stream) {
   if (p.seg_len <= 0) {
-    if (int rc = launch_scan_mode<T, PER_CHANNEL, SCAN_WHOLE>(p, num_requests, 1, stream)) return rc;
+    if (int rc = launch_scan_mode<T, DECAY, SCAN_WHOLE>(p, num_requests, 1, stream)) return rc;
   } else {
-    if (int rc = launch_scan_mode<T, PER_CHANNEL, SCAN_LOCAL>(p, num_requests, p.max_segments, stream)) return rc;
+    if (int rc = launch_scan_mode<T, DECAY, SCAN_LOCAL>(p, num_requests, p.max_segments, stream)) return rc;
     const int elements = DIM * p.vdim;
-    TS_LAUNCH("linear_attention_combine", linear_attention_combine_kernel<PER_CHANNEL>,
+    TS_LAUNCH("linear_attention_combine", linear_attention_combine_kernel<DECAY>,
               dim3(num_requests, p.H, (elements + 255) / 256), 256, 0, stream, p);
-    if (int rc = launch_scan_mode<T, PER_CHANNEL, SCAN_FROM_SEGMENT>(p, num_requests, p.max_segments, stream)) return rc;
+    if (int rc = launch_scan_mode<T, DECAY, SCAN_FROM_SEGMENT>(p, num_requests, p.max_segments, stream)) return rc;
   }
-  if (p.raw_out)
+  if (p.raw_out && p.finish)
     TS_LAUNCH("linear_attention_finish", linear_attention_finish_kernel<T>, num_tokens, p.H >= 8 ? 256 : 128, 0, stream, p,
               num_tokens);
   return 0;
@@ -471,28 +515,43 @@ TS_EXPORT int ts_linear_attention(int dtype, const void* q, long long ldq, const
                                   const void* norm_weight, int norm_weight_is_f32, float eps, void* out, long long ldo,
                                   int H, int vdim, int seg_len, float* seg_state, float* seg_decay, int max_segments,
                                   int num_tokens, float* raw_out, int in_act, int gate_act, int joint_norm,
-                                  cudaStream_t stream) {
+                                  const float* lower, int tied_key, const float* tok_keep, const float* tok_write,
+                                  int qk_group, int v_width, int finish, cudaStream_t stream) {
   TS_REQUIRE(num_requests > 0 && H > 0 && vdim > 0, "linear_attention: empty input");
   const int cols = block_columns(vdim);
   const int col_tiles = (vdim + cols - 1) / cols;
-  TS_REQUIRE((col_tiles > 1 || joint_norm) == (raw_out != nullptr) && num_tokens > 0,
-             "linear_attention: heads of more than %d value columns, and a norm over all heads, come with a 32-bit scratch "
-             "for their outputs, others without", cols);
-  TS_REQUIRE((z != nullptr) != (decay != nullptr), "linear_attention: either per-channel logits or per-head decays");
-  TS_REQUIRE(z == nullptr || tau > 0.f, "linear_attention: tau must be positive");
+  TS_REQUIRE((col_tiles > 1 || joint_norm || !finish) == (raw_out != nullptr) && num_tokens > 0,
+             "linear_attention: heads of more than %d value columns, a norm over all heads, and outputs that the caller "
+             "finishes, come with a 32-bit scratch for their outputs, others without", cols);
+  TS_REQUIRE((z != nullptr) + (decay != nullptr) + (tok_keep != nullptr) == 1,
+             "linear_attention: per-channel logits, per-head decays or per-token decays");
+  TS_REQUIRE(tok_keep == nullptr || tok_write != nullptr, "linear_attention: per-token decays come with per-token factors on k");
+  TS_REQUIRE(z == nullptr || lower != nullptr || tau > 0.f, "linear_attention: tau must be positive");
+  TS_REQUIRE(lower == nullptr || z != nullptr, "linear_attention: a lower bound belongs to per-channel logits");
+  TS_REQUIRE(!tied_key || (z != nullptr && rotary_dim == 0), "linear_attention: a tied key needs per-channel decays and no rotation");
+  TS_REQUIRE(qk_group >= 1 && H % qk_group == 0, "linear_attention: %d heads in groups of %d", H, qk_group);
+  TS_REQUIRE(v_width >= 1 && v_width <= vdim && (v_width == vdim || raw_out != nullptr),
+             "linear_attention: %d value columns in a state of %d (constant columns: the caller finishes)", v_width, vdim);
   TS_REQUIRE(rotary_dim >= 0 && rotary_dim <= DIM && rotary_dim % 2 == 0, "linear_attention: rotary_dim %d does not fit key size %d", rotary_dim, DIM);
   TS_REQUIRE(rotary_dim == 0 || (cos && sin && positions), "linear_attention: rotary without tables");
-  TS_REQUIRE(q && k && v && out && state && state_slots && fresh && cu_q, "linear_attention: a null operand");
+  TS_REQUIRE(q && (k || tied_key) && v && (out || !finish) && state && state_slots && fresh && cu_q, "linear_attention: a null operand");
   TS_REQUIRE(seg_len == 0 || (seg_len % CHUNK == 0 && seg_state && max_segments > 0 && max_segments <= 65535 &&
-                              (z == nullptr || seg_decay)),
+                              (decay != nullptr || seg_decay)),
              "linear_attention: segments of a multiple of %d tokens with scratch for their states", CHUNK);
-  ScanParams p{q, k, v, gate, ldq, ldk, ldv, ldg, z, ldz, decay, z ? 1.f / tau : 0.f, positions, cos, sin, rotary_dim,
+  ScanParams p{q, k, v, gate, ldq, ldk, ldv, ldg, z, ldz, decay, z && !lower ? 1.f / tau : 0.f, positions, cos, sin, rotary_dim,
                q_scale, k_scale, state, state_slots, fresh, cu_q, norm_weight, norm_weight_is_f32, eps, out, ldo, H, vdim,
-               seg_len, seg_state, seg_decay, max_segments, cols, col_tiles, raw_out, in_act, gate_act, joint_norm};
-  if (dtype == TS_F32)
-    return z ? launch_scan<float, true>(p, num_requests, num_tokens, stream) : launch_scan<float, false>(p, num_requests, num_tokens, stream);
-  if (dtype == TS_BF16)
-    return z ? launch_scan<__nv_bfloat16, true>(p, num_requests, num_tokens, stream)
-             : launch_scan<__nv_bfloat16, false>(p, num_requests, num_tokens, stream);
+               seg_len, seg_state, seg_decay, max_segments, cols, col_tiles, raw_out, in_act, gate_act, joint_norm,
+               lower, tied_key, tok_keep, tok_write, qk_group, v_width, finish};
+  const int mode = z ? DECAY_CHANNEL : (tok_keep ? DECAY_TOKEN : DECAY_HEAD);
+  if (dtype == TS_F32) {
+    if (mode == DECAY_CHANNEL) return launch_scan<float, DECAY_CHANNEL>(p, num_requests, num_tokens, stream);
+    if (mode == DECAY_TOKEN) return launch_scan<float, DECAY_TOKEN>(p, num_requests, num_tokens, stream);
+    return launch_scan<float, DECAY_HEAD>(p, num_requests, num_tokens, stream);
+  }
+  if (dtype == TS_BF16) {
+    if (mode == DECAY_CHANNEL) return launch_scan<__nv_bfloat16, DECAY_CHANNEL>(p, num_requests, num_tokens, stream);
+    if (mode == DECAY_TOKEN) return launch_scan<__nv_bfloat16, DECAY_TOKEN>(p, num_requests, num_tokens, stream);
+    return launch_scan<__nv_bfloat16, DECAY_HEAD>(p, num_requests, num_tokens, stream);
+  }
   return ts_fail("linear_attention: unknown dtype %d", dtype);
 }

@@ -514,11 +514,15 @@ def _latent_moe():
     return build.load_unit("latent_moe.cu")
 
 
+def _sequence():
+    return build.load_unit("sequence.cu")
+
+
 def units_for(head_dims, key_dims=()) -> list:
     """The (source, defines) units a model with these attention head sizes, and these key sizes of
     its matrix-state mixers, needs."""
     units = [("elementwise.cu", {}), ("gemm_simt.cu", {}), ("gemm_tcgen05.cu", {}), ("gemm_pair_tcgen05.cu", {}),
-             ("sampler.cu", {}), ("latent_moe.cu", {})]
+             ("sampler.cu", {}), ("latent_moe.cu", {}), ("sequence.cu", {})]
     units += [("attention_simt.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))]
     units += [("attention_mma.cu", _mma_defines(d)) for d in sorted(set(head_dims))
               if d <= MMA_MAX_HEAD_DIM]
@@ -863,9 +867,17 @@ def prefill_tile_queries(dtype, num_heads, num_kv_heads, head_dim, page_size=16)
     return 0
 
 
+#: the chunk mask and the distance bias live in the 32-bit attention kernel; the tensor-core kernels do not
+#: take them, so a mixer with either asks for no work lists
+BIASED_ATTENTION_ON_TENSOR_CORES = False
+
+
 def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None, backend=None, keep_first=0,
-                    sinks=None):
+                    sinks=None, chunk=0, slopes=None):
     """Attention of this step's queries over their requests' cached keys and values.
+    ``chunk`` > 0: a query at position i sees key j <= i only if i // chunk == j // chunk (chunks
+    count from position 0 of the sequence; no window beside it).  ``slopes`` float32 [H]: head h's
+    score of (i, j) loses slopes[h] * (i - j) after the scale.
     ``keep_first`` (with a window): the first keys of a sequence stay visible to every later query.
     ``sinks`` float32 [H]: head h's softmax sum holds one more term exp(sinks[h]) without key or value.
     q [T, H, D]; caches [pages, Hkv, page_size, D]; ``view`` a GroupView; ``ctx`` gives cu_q,
@@ -880,6 +892,13 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.shape != (H,) or not sinks.is_cuda):
         raise TypeError("paged_attention: sinks are float32 [heads] on the device")
     keep_first = int(keep_first) if window > 0 else 0
+    chunk = int(chunk or 0)
+    if chunk < 0 or (chunk and window > 0):
+        raise ValueError("paged_attention: a chunk is positive and comes without a window")
+    if slopes is not None and (slopes.dtype != torch.float32 or slopes.shape != (H,) or not slopes.is_cuda):
+        raise TypeError("paged_attention: slopes are float32 [heads] on the device")
+    if (chunk or slopes is not None) and backend is None:
+        chosen = "simt"         # the chunk mask and the distance bias live in the 32-bit kernel
     if backend is not None and backend != chosen:
         if q.dtype != torch.bfloat16 or (backend == "tcgen05") or (backend == "mma" and chosen == "simt"):
             raise ValueError(f"attention backend {backend!r} does not take {q.dtype}, head size {D}, pages of {page}")
@@ -942,12 +961,12 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             c_int(_tma_pages(k_cache, v_cache)), c_int(keep_first), _ptr(sinks), _stream()), launches)
         return out
     lib = _attention(D)
-    _check(lib, lib.ts_paged_attention(
+    _check(lib, lib.ts_paged_attention_biased(
         c_int(_dt(q)), _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table),
         _ptr(ctx.cu_q), _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len),
         c_int(H), c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)),
         c_float(scale), c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), c_int(keep_first),
-        _ptr(sinks), _stream()),
+        _ptr(sinks), c_int(chunk), _ptr(slopes), _stream()),
         launches)
     return out
 
@@ -1288,7 +1307,9 @@ def _linear_attention(key_dim: int):
 
 def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, out_dtype, *, decay=None,
                      decay_logits=None, tau=1.0, rotary=None, q_scale=1.0, k_scale=1.0, norm_weight=None, eps=0.0,
-                     segment=None, input_activation=None, gate_activation="silu", joint_norm=False):
+                     segment=None, input_activation=None, gate_activation="silu", joint_norm=False,
+                     lower=None, tied_key=False, token_keep=None, token_write=None, qk_group=1, value_width=None,
+                     raw=False):
     """Per request and head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over this step's
     tokens, from and to ``state`` [slots, H, key_dim, value_dim] (float32) at the requests' state
     slots (``ctx.state_slots``, ``ctx.fresh``, ``ctx.cu_q``); returns [T, H * value_dim] =
@@ -1299,27 +1320,47 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
     segment of the side-by-side form (None: chosen by the step's longest portion, 0: never).
     ``input_activation`` "silu": q, k and v pass through silu first.  ``gate_activation`` "sigmoid":
     the output is multiplied by sigmoid(gate).  ``joint_norm``: the output norm runs over all heads
-    of a token together, with ``norm_weight`` [H * value_dim]."""
-    if input_activation not in (None, "silu") or gate_activation not in ("silu", "sigmoid"):
-        raise ValueError("linear_attention: input activation None or silu, gate activation silu or sigmoid")
-    _cuda(q, k, v, gate, state, decay, decay_logits, norm_weight)
+    of a token together, with ``norm_weight`` [H * value_dim].  ``input_activation`` may also name
+    the operands that pass through silu, as a string of the letters q, k, v.
+    ``lower`` float32 [H * key_dim] (with ``decay_logits``): a = lower + (1 - lower) sigmoid(z); with
+    ``tied_key`` k = 1 - a and ``k`` is None.  ``token_keep`` / ``token_write`` float32 [T, H]: the decay of
+    (token, head) and a factor on its k, S_t = keep_t S_(t-1) + write_t k_t v_t^T.  ``qk_group``: heads
+    that share one q and one k (q, k [T, H / qk_group * key_dim]).  ``value_width`` < value_dim: v holds
+    that many columns per head, the state's next column is fed ones (so that column of S^T q is
+    sum of the k . q terms) and the rest zeros.  ``raw``: returns the 32-bit S^T q [T, H * value_dim]
+    without norm and gate, for a finishing kernel of the caller's."""
+    acts = {None: 0, "silu": 7}
+    if isinstance(input_activation, str) and input_activation != "silu" and set(input_activation) <= set("qkv"):
+        acts[input_activation] = sum({"q": 1, "k": 2, "v": 4}[c] for c in set(input_activation))
+    if input_activation not in acts or gate_activation not in ("silu", "sigmoid"):
+        raise ValueError("linear_attention: input activation None, silu or letters of qkv, gate activation silu or sigmoid")
+    _cuda(q, k, v, gate, state, decay, decay_logits, norm_weight, lower, token_keep, token_write)
     T = q.shape[0]
     H = num_heads
-    if q.shape[1] != H * key_dim or k.shape[1] != H * key_dim or v.shape[1] != H * value_dim:
+    vw = value_dim if value_width is None else int(value_width)
+    if H % qk_group or q.shape[1] != H // qk_group * key_dim or (k is not None and k.shape[1] != q.shape[1]) \
+            or v.shape[1] != H * vw or (k is None) != bool(tied_key):
         raise ValueError("linear_attention: q, k, v do not have heads x size columns")
     if state.dtype != torch.float32 or tuple(state.shape[1:]) != (H, key_dim, value_dim) or not state.is_contiguous():
         raise TypeError("linear_attention: the state is contiguous float32 [slots, H, key_dim, value_dim]")
-    if (decay is None) == (decay_logits is None):
-        raise ValueError("linear_attention: either per-head decays or per-channel logits")
+    if (decay is not None) + (decay_logits is not None) + (token_keep is not None) != 1:
+        raise ValueError("linear_attention: per-head decays, per-channel logits or per-token decays")
     if decay_logits is not None and (decay_logits.dtype != torch.float32 or decay_logits.shape[1] != H * key_dim):
         raise TypeError("linear_attention: decay logits are float32 [T, H * key_dim]")
-    out = torch.empty(T, H * value_dim, dtype=out_dtype, device=q.device)
+    if lower is not None and (lower.dtype != torch.float32 or lower.numel() != H * key_dim or decay_logits is None):
+        raise TypeError("linear_attention: the lower bounds are float32 [H * key_dim] and belong to decay logits")
+    for name, t in (("token_keep", token_keep), ("token_write", token_write)):
+        if token_keep is not None and (t is None or t.dtype != torch.float32 or tuple(t.shape) != (T, H) or not t.is_contiguous()):
+            raise TypeError(f"linear_attention: {name} is contiguous float32 [T, H]")
+    if vw != value_dim and not raw:
+        raise ValueError("linear_attention: constant value columns come with raw outputs")
+    out = None if raw else torch.empty(T, H * value_dim, dtype=out_dtype, device=q.device)
     zp, zld = _columns(decay_logits) if decay_logits is not None else (c_void_p(0), c_longlong(0))
     gp, gld = _columns(gate) if gate is not None else (c_void_p(0), c_longlong(0))
     lib = _linear_attention(key_dim)
     # a head of more value columns than a block takes: its output norm runs as a kernel of its own
     tiles = lib.ts_linear_attention_column_tiles(c_int(value_dim))
-    wide = tiles > 1 or bool(joint_norm)
+    wide = tiles > 1 or bool(joint_norm) or bool(raw)
     if segment is None:
         seg_len = linear_attention_segment(getattr(ctx, "max_q_len", 0), H * tiles,
                                            lib.ts_linear_attention_resident_blocks(c_int(value_dim)))
@@ -1329,20 +1370,24 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
     if seg_len:
         max_segments = -(-(getattr(ctx, "max_q_len", 0) or T) // seg_len)
         seg_state = torch.empty(ctx.num_requests * H * max_segments * key_dim * value_dim, dtype=torch.float32, device=q.device)
-        if decay_logits is not None:
+        if decay is None:
             seg_decay = torch.empty(ctx.num_requests * H * max_segments * key_dim, dtype=torch.float32, device=q.device)
-    raw = torch.empty(T, H * value_dim, dtype=torch.float32, device=q.device) if wide else None
+    raw_out = torch.empty(T, H * value_dim, dtype=torch.float32, device=q.device) if wide else None
+    kp, kld = _columns(k) if k is not None else (c_void_p(0), c_longlong(0))
     _check(lib, lib.ts_linear_attention(
-        c_int(_dt(q)), *_columns(q), *_columns(k), *_columns(v), gp, gld, zp, zld, c_float(tau), _ptr(decay),
+        c_int(_dt(q)), *_columns(q), kp, kld, *_columns(v), gp, gld, zp, zld, c_float(tau), _ptr(decay),
         _ptr(ctx.positions), _ptr(rotary.cos if rotary is not None else None),
         _ptr(rotary.sin if rotary is not None else None), c_int(rotary.rotary_dim if rotary is not None else 0),
         c_float(q_scale), c_float(k_scale), _ptr(state), _ptr(ctx.state_slots), _ptr(ctx.fresh), _ptr(ctx.cu_q),
         c_int(ctx.num_requests), _ptr(norm_weight), c_int(_vec_flag(norm_weight, out_dtype) if norm_weight is not None else 0),
-        c_float(eps), _ptr(out), c_longlong(out.stride(0)), c_int(H), c_int(value_dim), c_int(seg_len), _ptr(seg_state),
-        _ptr(seg_decay), c_int(max_segments), c_int(T), _ptr(raw), c_int(1 if input_activation == "silu" else 0),
-        c_int(1 if gate_activation == "sigmoid" else 0), c_int(1 if joint_norm else 0), _stream()),
-        (3 if seg_len else 1) + int(wide))
-    return out
+        c_float(eps), _ptr(out), c_longlong(out.stride(0) if out is not None else 0), c_int(H), c_int(value_dim),
+        c_int(seg_len), _ptr(seg_state),
+        _ptr(seg_decay), c_int(max_segments), c_int(T), _ptr(raw_out), c_int(acts[input_activation]),
+        c_int(1 if gate_activation == "sigmoid" else 0), c_int(1 if joint_norm else 0), _ptr(lower),
+        c_int(1 if tied_key else 0), _ptr(token_keep), _ptr(token_write), c_int(qk_group), c_int(vw),
+        c_int(0 if raw else 1), _stream()),
+        (3 if seg_len else 1) + int(wide and not raw))
+    return raw_out if raw else out
 
 
 # ----------------------------------------------------------------------------- a block that norms what its sub-layers return
@@ -1494,7 +1539,7 @@ def moe_activate_(a, gates, num_experts, logits=None, top=0):
 MOE_GROUPED_MIN_TOKENS = 256
 
 
-def moe_grouped(h, gates, up, down_side_by_side, top):
+def moe_grouped(h, gates, up, down_side_by_side, top, gated=False):
     """Mixture of experts over rows sorted by expert.  h [T, n] bfloat16; gates float32 [T, E] (zero:
     not chosen); up [E ff, n] (expert by expert); down_side_by_side [n, E ff].  Returns [T, n]:
     sum over a token's experts of gate * W_down,e relu(W_up,e h)^2, the sum in 32-bit.  The two
@@ -1502,7 +1547,7 @@ def moe_grouped(h, gates, up, down_side_by_side, top):
     _cuda(h, gates, up, down_side_by_side)
     T, n = h.shape
     E = gates.shape[1]
-    ff = up.shape[0] // E
+    ff = up.shape[0] // E // (2 if gated else 1)
     lib = _latent_moe()
     align = lib.ts_moe_group_align()
     capacity = -(-(T * top + E * (align - 1)) // align) * align + align
@@ -1512,11 +1557,249 @@ def moe_grouped(h, gates, up, down_side_by_side, top):
                                  _stream()))
     x = torch.empty(capacity, n, dtype=h.dtype, device=h.device)
     _check(lib, lib.ts_moe_gather(c_int(_dt(h)), _ptr(h), _ptr(row_token), _ptr(x), c_int(capacity), c_int(n), _stream()))
-    a = torch.nn.functional.grouped_mm(x, up.view(E, ff, n).transpose(1, 2), offs=ends)
-    _check(lib, lib.ts_moe_activate(c_int(_dt(a)), _ptr(a), None, c_int(capacity), c_int(1), c_int(ff), None, c_int(0), _stream()))
+    if gated:
+        a = moe_gated_activate(torch.nn.functional.grouped_mm(x, up.view(E, 2 * ff, n).transpose(1, 2), offs=ends), None, 1)
+    else:
+        a = torch.nn.functional.grouped_mm(x, up.view(E, ff, n).transpose(1, 2), offs=ends)
+        _check(lib, lib.ts_moe_activate(c_int(_dt(a)), _ptr(a), None, c_int(capacity), c_int(1), c_int(ff), None, c_int(0), _stream()))
     y = torch.nn.functional.grouped_mm(a, down_side_by_side.view(n, E, ff).permute(1, 2, 0), offs=ends)
     out = torch.empty(T, n, dtype=h.dtype, device=h.device)
     _check(lib, lib.ts_moe_combine(c_int(_dt(y)), _ptr(y), _ptr(gates), _ptr(pair_row), _ptr(out), c_int(T), c_int(E), c_int(n),
                                    _stream()))
     count_launches(2)
+    return out
+
+
+# ----------------------------------------------------------------------------- rows that depend on their neighbours in time
+def _f32(t) -> int:
+    if t.dtype == torch.float32:
+        return 1
+    if t.dtype == torch.bfloat16:
+        return 0
+    raise TypeError(f"unsupported dtype {t.dtype}; kernels take float32 and bfloat16")
+
+
+def add_position_rows_(residual, table, positions):
+    """residual float32 [T, n] (in place) += table[positions] (a learned vector per position)."""
+    _cuda(residual, table, positions)
+    T, n = residual.shape
+    if residual.dtype != torch.float32 or not residual.is_contiguous() or table.shape[1] != n or not table.is_contiguous():
+        raise TypeError("add_position_rows: the residual is contiguous float32 and the table has its width")
+    lib = _sequence()
+    _check(lib, lib.ts_add_position_rows(_ptr(residual), _ptr(table), c_int(_f32(table)), _ptr(positions),
+                                         c_int(table.shape[0]), c_int(T), c_int(n), _stream()))
+    return residual
+
+
+CAUSAL_CONV_MAX_TAPS = 8
+
+
+def causal_conv(x, weight, state, ctx, out_dtype, bias=None, add_input=False, activation=None):
+    """Causal convolution over time on every channel: y_t = sum_j weight[:, j] x_(t - taps + 1 + j)
+    (+ bias), zeros before a sequence's start, then silu with ``activation`` "silu", then + x_t with
+    ``add_input``.  x [T, C] float32 or of the compute type (a column range is fine); weight
+    [C, taps]; ``state`` float32 [slots, taps - 1, C] holds every request's last inputs between
+    steps (``ctx.state_slots``, ``ctx.fresh``, ``ctx.cu_q``) and is brought up to date.  Returns
+    [T, C] of ``out_dtype``."""
+    _cuda(x, weight, bias, state)
+    T, C = x.shape
+    taps = weight.shape[1]
+    if weight.shape[0] != C or not weight.is_contiguous() or x.stride(1) != 1 or activation not in (None, "silu"):
+        raise ValueError("causal_conv: weight [channels, taps], x contiguous along its rows, activation None or silu")
+    if not 1 <= taps <= CAUSAL_CONV_MAX_TAPS:
+        raise ValueError(f"causal_conv: 1 to {CAUSAL_CONV_MAX_TAPS} taps, got {taps}")
+    if taps > 1 and (state.dtype != torch.float32 or tuple(state.shape[1:]) != (taps - 1, C) or not state.is_contiguous()):
+        raise TypeError("causal_conv: the state is contiguous float32 [slots, taps - 1, channels]")
+    if bias is not None and (bias.dtype != weight.dtype or bias.shape != (C,)):
+        raise TypeError("causal_conv: the bias is [channels] of the weight's dtype")
+    out = torch.empty(T, C, dtype=out_dtype, device=x.device)
+    lib = _sequence()
+    _check(lib, lib.ts_causal_conv(
+        _ptr(x), c_longlong(x.stride(0)), c_int(_f32(x)), _ptr(out), c_longlong(C), c_int(_f32(out)), _ptr(weight),
+        c_int(_f32(weight)), _ptr(bias), c_int(taps), _ptr(state), _ptr(ctx.state_slots), _ptr(ctx.fresh), _ptr(ctx.cu_q),
+        c_int(ctx.num_requests), c_int(max(1, min(ctx.max_q_len or T, T))), c_int(C), c_int(1 if add_input else 0),
+        c_int(1 if activation == "silu" else 0), _stream()))
+    return out
+
+
+def group_norm(x, weight, groups, eps, out_dtype, rows=None):
+    """Every one of ``groups`` equal consecutive parts of a row divided by its own root mean
+    square, the row times ``weight``.  x [T, n] float32 or of the compute type; with ``rows``
+    (int32) only those rows, in that order."""
+    _cuda(x, weight, rows)
+    n = x.shape[1]
+    if x.stride(1) != 1 or weight.shape != (n,) or n % groups:
+        raise ValueError(f"group_norm: {n} columns in {groups} groups")
+    num_out = x.shape[0] if rows is None else rows.shape[0]
+    out = torch.empty(num_out, n, dtype=out_dtype, device=x.device)
+    lib = _sequence()
+    _check(lib, lib.ts_group_norm(_ptr(x), c_longlong(x.stride(0)), c_int(_f32(x)), _ptr(weight), c_int(_f32(weight)),
+                                  _ptr(rows), c_int(groups), c_int(n), c_float(eps), _ptr(out), c_int(_f32(out)),
+                                  c_int(num_out), _stream()))
+    return out
+
+
+def group_norm_add_(y, weight, groups, eps, residual):
+    """residual float32 [T, n] (in place) += group_norm(y) * weight: the sum stays 32-bit."""
+    y = materialize(y)
+    _cuda(y, weight, residual)
+    T, n = residual.shape
+    if residual.dtype != torch.float32 or not residual.is_contiguous() or tuple(y.shape) != (T, n) or y.stride(1) != 1 \
+            or weight.shape != (n,) or n % groups:
+        raise ValueError(f"group_norm_add: the residual is contiguous float32 [T, {n}], y of its shape, {groups} groups")
+    lib = _sequence()
+    _check(lib, lib.ts_group_norm_add(_ptr(y), c_longlong(y.stride(0)), c_int(_f32(y)), _ptr(weight), c_int(_f32(weight)),
+                                      c_int(groups), c_int(n), c_float(eps), _ptr(residual), c_int(T), _stream()))
+    return residual
+
+
+def axpby(a, x, b, y):
+    """a x + b y for two contiguous tensors alike in shape and dtype (32-bit arithmetic)."""
+    x, y = materialize(x), materialize(y)
+    _cuda(x, y)
+    if x.shape != y.shape or x.dtype != y.dtype or not x.is_contiguous() or not y.is_contiguous():
+        raise TypeError("axpby: operands are contiguous and alike in shape and dtype")
+    out = torch.empty_like(x)
+    lib = _sequence()
+    _check(lib, lib.ts_axpby(_ptr(x), _ptr(y), c_int(_f32(x)), c_float(a), c_float(b), _ptr(out), c_int(_f32(out)),
+                             c_longlong(x.numel()), _stream()))
+    return out
+
+
+def gate_columns(attn, gate, vdim):
+    """[T, H * vdim] = attn [T, H, D][..., :vdim] * sigmoid(gate [T, H * vdim]), element by element;
+    ``gate`` may be a column range."""
+    _cuda(attn, gate)
+    T, H, D = attn.shape
+    if not attn.is_contiguous() or gate.shape != (T, H * vdim) or gate.stride(1) != 1 or gate.dtype != attn.dtype:
+        raise ValueError("gate_columns: operands do not fit")
+    out = torch.empty(T, H * vdim, dtype=attn.dtype, device=attn.device)
+    lib = _sequence()
+    _check(lib, lib.ts_gate_columns(_ptr(attn), _ptr(gate), c_longlong(gate.stride(0)), c_int(_f32(attn)), _ptr(out), c_int(H),
+                                    c_int(D), c_int(vdim), c_int(T), _stream()))
+    return out
+
+
+def joint_norm_kvwrite(q, k, v, num_heads, num_kv_heads, dim, vdim, stored_dim, q_weight=None, k_weight=None, eps=0.0,
+                       k_cache=None, v_cache=None, slot_mapping=None, page_size=0):
+    """q [T, H dim] and k [T, Hkv dim] each divided by the root mean square over the whole row (all
+    heads at once) and multiplied by a weight per column (both weights None: no norm); q goes to a
+    [T, H, stored_dim] tensor (returned), k and v [T, Hkv vdim] to the cache slots of
+    ``slot_mapping`` (None: nothing is written), heads padded with zeros to ``stored_dim``."""
+    _cuda(q, k, v, q_weight, k_weight, k_cache, v_cache, slot_mapping)
+    T = q.shape[0]
+    if q.shape[1] != num_heads * dim or k.shape[1] != num_kv_heads * dim or v.shape[1] != num_kv_heads * vdim:
+        raise ValueError("joint_norm_kvwrite: q, k, v do not have heads x size columns")
+    if k_cache is not None and (k_cache.dtype != q.dtype or k_cache.shape[-1] != stored_dim or not k_cache.is_contiguous()
+                                or not v_cache.is_contiguous()):
+        raise TypeError("joint_norm_kvwrite: the cache does not fit the activations")
+    if (q_weight is None) != (k_weight is None) or (q_weight is not None and q_weight.dtype != k_weight.dtype):
+        raise TypeError("joint_norm_kvwrite: q and k are normed together, with weights of one dtype")
+    out = torch.empty(T, num_heads, stored_dim, dtype=q.dtype, device=q.device)
+    lib = _sequence()
+    _check(lib, lib.ts_joint_norm_kvwrite(
+        c_int(_f32(q)), *_columns(q), *_columns(k), *_columns(v), _ptr(q_weight), _ptr(k_weight),
+        c_int(_f32(q_weight) if q_weight is not None else 0), c_float(eps), c_int(num_heads), c_int(num_kv_heads),
+        c_int(dim), c_int(vdim), c_int(stored_dim), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping),
+        c_int(page_size), c_int(T), _stream()))
+    return out
+
+
+def mlstm_gates(raw, cap, m_state, ctx, num_heads):
+    """The stabilised gates of a matrix memory with an exponential input gate.  raw float32
+    [T, 2 H]: input-gate logits, then forget-gate logits.  i = cap tanh(. / cap),
+    f = logsigmoid(cap tanh(. / cap)), m_t = max(f_t + m_(t-1), i_t) with m in ``m_state`` float32
+    [slots, H] (zero for a request that starts).  Returns float32 [T, H] each: keep =
+    exp(f + m_(t-1) - m_t), write = exp(i - m_t), floor = exp(-m_t)."""
+    _cuda(raw, m_state)
+    T, H = raw.shape[0], num_heads
+    if raw.dtype != torch.float32 or raw.shape[1] != 2 * H or raw.stride(1) != 1 or m_state.dtype != torch.float32 \
+            or tuple(m_state.shape[1:]) != (H,) or not m_state.is_contiguous():
+        raise TypeError("mlstm_gates: raw float32 [T, 2 H], m float32 [slots, H]")
+    keep, write, floor = (torch.empty(T, H, dtype=torch.float32, device=raw.device) for _ in range(3))
+    lib = _sequence()
+    _check(lib, lib.ts_mlstm_gates(_ptr(raw), c_longlong(raw.stride(0)), c_float(cap), _ptr(m_state), _ptr(ctx.state_slots),
+                                   _ptr(ctx.fresh), _ptr(ctx.cu_q), c_int(ctx.num_requests), c_int(H), _ptr(keep), _ptr(write),
+                                   _ptr(floor), _stream()))
+    return keep, write, floor
+
+
+def ssm_gates(dt_raw, dt_bias, a_log, num_heads):
+    """dt = softplus(dt_raw + dt_bias); returns float32 [T, H] keep = exp(-exp(a_log) dt) and write = dt."""
+    _cuda(dt_raw, dt_bias, a_log)
+    T, H = dt_raw.shape[0], num_heads
+    if dt_raw.shape[1] != H or dt_raw.stride(1) != 1 or dt_bias.shape != (H,) or a_log.shape != (H,) or dt_bias.dtype != a_log.dtype:
+        raise TypeError("ssm_gates: dt_raw [T, H], dt_bias and a_log [H] of one dtype")
+    keep, write = (torch.empty(T, H, dtype=torch.float32, device=dt_raw.device) for _ in range(2))
+    lib = _sequence()
+    _check(lib, lib.ts_ssm_gates(_ptr(dt_raw), c_longlong(dt_raw.stride(0)), c_int(_f32(dt_raw)), _ptr(dt_bias), _ptr(a_log),
+                                 c_int(_f32(a_log)), c_int(H), c_int(T), _ptr(keep), _ptr(write), _stream()))
+    return keep, write
+
+
+def mlstm_finish(raw, floor, weight, gate, eps, num_heads, value_dim, out_dtype):
+    """raw float32 [T, H, wide]: columns [0, value_dim) the numerators, column value_dim the
+    normaliser n . q.  Returns [T, H value_dim]: numerator / (max(|n . q|, floor) + 1e-6), divided by
+    its root mean square per head, times weight [H value_dim], times sigmoid(gate)."""
+    _cuda(raw, floor, weight, gate)
+    T, H = floor.shape
+    wide = raw.shape[1] // H
+    if raw.dtype != torch.float32 or not raw.is_contiguous() or H != num_heads or wide <= value_dim or gate.stride(1) != 1:
+        raise TypeError("mlstm_finish: operands do not fit")
+    out = torch.empty(T, H * value_dim, dtype=out_dtype, device=raw.device)
+    lib = _sequence()
+    _check(lib, lib.ts_mlstm_finish(_ptr(raw), c_int(wide), _ptr(floor), _ptr(weight), c_int(_f32(weight)), _ptr(gate),
+                                    c_longlong(gate.stride(0)), c_int(_f32(out)), c_float(eps), _ptr(out), c_int(H),
+                                    c_int(value_dim), c_int(T), _stream()))
+    return out
+
+
+def ssm_finish(raw, x, skip, z, weight, groups, eps, num_heads, value_dim, out_dtype):
+    """(raw + skip[h] x) silu(z), RMS-normed in ``groups`` equal parts over all heads, times weight.
+    raw float32 [T, H value_dim]; x, z [T, H value_dim] of the compute type (column ranges are fine)."""
+    _cuda(raw, x, skip, z, weight)
+    T = raw.shape[0]
+    n = num_heads * value_dim
+    if raw.dtype != torch.float32 or not raw.is_contiguous() or raw.shape[1] != n or x.shape[1] != n or z.shape[1] != n \
+            or x.stride(1) != 1 or z.stride(1) != 1 or skip.dtype != weight.dtype or n % groups:
+        raise TypeError("ssm_finish: operands do not fit")
+    out = torch.empty(T, n, dtype=out_dtype, device=raw.device)
+    lib = _sequence()
+    _check(lib, lib.ts_ssm_finish(_ptr(raw), _ptr(x), c_longlong(x.stride(0)), _ptr(skip), _ptr(z), c_longlong(z.stride(0)),
+                                  _ptr(weight), c_int(_f32(weight)), c_int(_f32(out)), c_int(groups), c_float(eps), _ptr(out),
+                                  c_int(num_heads), c_int(value_dim), c_int(T), _stream()))
+    return out
+
+
+# ----------------------------------------------------------------------------- experts chosen by scores with a correction
+def moe_route_scored(logits, correction, top, groups=1, keep=1):
+    """float32 [T, E] router logits -> float32 [T, E] weights: s = sigmoid(z) for the ``top`` experts
+    with the largest s + correction among the experts of the ``keep`` best of ``groups`` equal groups
+    of neighbours (a group's score: the sum of its two largest s + correction), zero elsewhere."""
+    _cuda(logits, correction)
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise TypeError("moe_route_scored: router logits are contiguous float32")
+    T, E = logits.shape
+    if correction is not None and (correction.dtype != torch.float32 or correction.shape != (E,)):
+        raise TypeError("moe_route_scored: the correction is float32 [experts]")
+    gates = torch.empty_like(logits)
+    lib = _latent_moe()
+    _check(lib, lib.ts_moe_route_scored(_ptr(logits), _ptr(correction), _ptr(gates), c_int(T), c_int(E), c_int(top),
+                                        c_int(groups), c_int(keep), _stream()))
+    return gates
+
+
+def moe_gated_activate(a, gates, num_experts):
+    """a [rows, E * 2 ff] (per expert: gate rows, then up rows) -> [rows, E * ff] =
+    silu(gate) * up * gates[row, e]; ``gates`` None: no weight (rows that are sorted by expert)."""
+    _cuda(a, gates)
+    rows = a.shape[0]
+    ff = a.shape[1] // (2 * num_experts)
+    if not a.is_contiguous() or a.shape[1] != 2 * ff * num_experts or \
+            (gates is not None and (gates.shape != (rows, num_experts) or gates.dtype != torch.float32 or not gates.is_contiguous())):
+        raise ValueError("moe_gated_activate: operands do not fit")
+    out = torch.empty(rows, num_experts * ff, dtype=a.dtype, device=a.device)
+    lib = _latent_moe()
+    _check(lib, lib.ts_moe_gated_activate(c_int(_dt(a)), _ptr(a), _ptr(gates), c_int(rows), c_int(num_experts), c_int(ff),
+                                          _ptr(out), _stream()))
     return out

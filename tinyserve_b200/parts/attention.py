@@ -17,7 +17,15 @@ to what the attention kernels take), padded with zeros: zero key columns add not
 and the padded output columns are dropped.
 
 With a window, ``keep_first`` > 0 keeps the first tokens of every sequence visible to all later
-queries (they keep their own positions, and their pages are never released)."""
+queries (they keep their own positions, and their pages are never released).
+
+Further forms, each a parameter: ``joint_norm`` (q and k each divided by the root mean square over
+all their heads at once, before they are split into heads, with one weight per column, plain);
+``chunk`` > 0 (position i sees j <= i only if i // chunk == j // chunk, chunks counted from
+position 0 of the sequence); ``distance_slopes`` (one slope per head: slope * (i - j) is taken off
+the scaled score); ``sinks`` (a learned number per head whose exponential joins the softmax sum,
+without key or value); ``out_gate`` (the concatenated heads times sigmoid(W_g h), element by
+element, before the output projection).  Biases on q, k and v go with all of them."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -26,7 +34,7 @@ from .base import (CacheSpec, Mixer, ParamSpec, Source, build_norm, build_positi
 
 
 DEFAULT_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm",
-                 "gate": "g_proj"}
+                 "gate": "g_proj", "sinks": "sinks"}
 
 
 class Attention(Mixer):
@@ -35,7 +43,8 @@ class Attention(Mixer):
 
     def __init__(self, hidden_size, num_heads, num_kv_heads, head_dim, bias=False, qk_norm=None,
                  position=None, window=0, scale=None, names=None, value_dim=None, unit_norm_eps=None,
-                 head_gate=False, keep_first=0):
+                 head_gate=False, keep_first=0, joint_norm=False, norm_eps=0.0, chunk=0, distance_slopes=None,
+                 sinks=False, out_gate=False):
         super().__init__()
         self.names = dict(DEFAULT_NAMES, **(names or {}))
         if num_heads % num_kv_heads:
@@ -54,17 +63,30 @@ class Attention(Mixer):
             raise ValueError("attention: keep_first must not be negative")
         #: the plain form runs the kernels that fuse per-head norm, rotary and cache write (and, for
         #: a few decoded tokens, the attention itself); the general form has kernels of its own
+        self.joint_norm, self.norm_eps, self.chunk = bool(joint_norm), float(norm_eps), int(chunk or 0)
+        self.slope_values = tuple(float(x) for x in distance_slopes) if distance_slopes is not None else None
+        self.has_sinks, self.out_gate = bool(sinks), bool(out_gate)
+        if self.chunk < 0 or (self.chunk and self.window):
+            raise ValueError("attention: a chunk is positive and comes without a window")
+        if self.slope_values is not None and len(self.slope_values) != num_heads:
+            raise ValueError(f"attention: {len(self.slope_values)} slopes for {num_heads} heads")
+        if self.out_gate and self.head_gate:
+            raise ValueError("attention: one gate, per head or per element")
+        extended = self.joint_norm or self.chunk > 0 or self.slope_values is not None or self.has_sinks or self.out_gate
         self.general = (self.value_dim != head_dim or self.unit_norm_eps is not None or self.head_gate
-                        or self.keep_first > 0)
-        if self.general and (qk_norm is not None or bias):
+                        or self.keep_first > 0 or extended)
+        if self.general and (qk_norm is not None or (bias and not extended)):
             raise ValueError("attention: a value size of its own, the unit norm and the head gate come "
                              "without a weighted q/k norm and without biases")
+        if self.joint_norm and (self.unit_norm_eps is not None or position is not None):
+            raise ValueError("attention: the norm over all heads comes without rotation and without the unit norm")
+        self.slopes = self.sinks = None
         widest = max(head_dim, self.value_dim)
         self.stored_dim = -(-widest // 16) * 16 if self.general else head_dim
         self.q_size = num_heads * head_dim
         self.kv_size = num_kv_heads * head_dim
         self.v_size = num_kv_heads * self.value_dim
-        self.gate_size = num_heads if self.head_gate else 0
+        self.gate_size = num_heads if self.head_gate else (num_heads * self.value_dim if self.out_gate else 0)
 
     def children(self):
         out = {}
@@ -78,7 +100,7 @@ class Attention(Mixer):
         q, kv, vs = self.q_size, self.kv_size, self.v_size
         nm = self.names
         rows = ((nm["q"], 0, q), (nm["k"], q, q + kv), (nm["v"], q + kv, q + kv + vs))
-        if self.head_gate:
+        if self.gate_size:
             rows += ((nm["gate"], q + kv + vs, q + kv + vs + self.gate_size),)
         specs = {
             "qkv_proj.weight": ParamSpec((q + kv + vs + self.gate_size, self.hidden_size), sources=tuple(
@@ -88,25 +110,67 @@ class Attention(Mixer):
         }
         if self.bias:
             # drawn like a matrix in the random-weights mode: a bias of zeros would hide a fault
-            specs["qkv_proj.bias"] = ParamSpec((q + 2 * kv,), role="matrix", init="normal", sources=tuple(
-                Source(f"{n}.bias", a, b) for n, a, b in rows))
+            # (the gate's rows, where there are any, have no bias: ``bind`` zeroes theirs)
+            specs["qkv_proj.bias"] = ParamSpec((q + kv + vs + self.gate_size,), role="matrix", init="normal", sources=tuple(
+                Source(f"{n}.bias", a, b) for n, a, b in rows[:3]))
+        if self.joint_norm:
+            specs["q_norm.weight"] = ParamSpec((q,), role="vector", init="norm_weight",
+                                               sources=(Source(f"{nm['q_norm']}.weight", 0, q),))
+            specs["k_norm.weight"] = ParamSpec((kv,), role="vector", init="norm_weight",
+                                               sources=(Source(f"{nm['k_norm']}.weight", 0, kv),))
+        if self.has_sinks:
+            specs["sinks"] = ParamSpec((self.num_heads,), role="vector", init="wide", sources=(Source(nm["sinks"], 0, self.num_heads),))
         return specs
+
+    def bind(self, tensors):
+        tensors = dict(tensors)
+        if self.bias and self.gate_size and "qkv_proj.bias" in tensors:
+            tensors["qkv_proj.bias"][self.q_size + self.kv_size + self.v_size:] = 0
+        if "sinks" in tensors:
+            tensors["sinks"] = tensors["sinks"].float().contiguous()       # they join a 32-bit sum
+        super().bind(tensors)
+
+    def prepare(self, runtime):
+        super().prepare(runtime)
+        if self.slope_values is not None:
+            import torch
+            self.slopes = torch.tensor(self.slope_values, dtype=torch.float32, device=runtime.device)
 
     def cache_spec(self):
         kind = "window" if self.window > 0 else "full"
         return CacheSpec(kind, self.num_kv_heads, self.stored_dim, self.window, keep_first=self.keep_first)
 
+    def _biased(self):
+        return self.chunk > 0 or self.slope_values is not None
+
     accepts_scaled_rows = True
 
     def work_tile_queries(self, dtype, page_size):
+        if self._biased() and not ops.BIASED_ATTENTION_ON_TENSOR_CORES:
+            return 0
         return ops.prefill_tile_queries(dtype, self.num_heads, self.num_kv_heads, self.stored_dim, page_size)
 
     def _forward_general(self, h, ctx, call):
-        qkv = ops.materialize(ops.linear(h, self.w["qkv_proj.weight"]))
+        qkv = ops.materialize(ops.linear(h, self.w["qkv_proj.weight"], self.w.get("qkv_proj.bias")))
         q_end, k_end = self.q_size, self.q_size + self.kv_size
         v_end = k_end + self.v_size
         cache = ctx.cache(call.cache)
         view = ctx.group(cache.group)
+        if self.joint_norm or self._biased() or self.has_sinks or self.out_gate:
+            q = ops.joint_norm_kvwrite(
+                qkv[:, :q_end], qkv[:, q_end:k_end], qkv[:, k_end:v_end], self.num_heads, self.num_kv_heads, self.head_dim,
+                self.value_dim, self.stored_dim, self.w.get("q_norm.weight"), self.w.get("k_norm.weight"), self.norm_eps,
+                k_cache=cache.k, v_cache=cache.v, slot_mapping=view.slot_mapping if call.writes_cache else None,
+                page_size=view.page_size)
+            out = ops.paged_attention(q, cache.k, cache.v, view, ctx, self.scale, self.window, keep_first=self.keep_first,
+                                      sinks=self.w.get("sinks"), chunk=self.chunk, slopes=self.slopes)
+            if self.out_gate:
+                out = ops.gate_columns(out, qkv[:, v_end:], self.value_dim)
+            elif self.head_gate or self.stored_dim != self.value_dim:
+                out = ops.head_gate(out, qkv[:, v_end:] if self.head_gate else None, self.value_dim)
+            else:
+                out = out.view(out.shape[0], self.num_heads * self.value_dim)
+            return ops.linear(out, self.w["o_proj.weight"], allow_pending=True)
         q = ops.rope_unit_kvwrite(
             qkv[:, :q_end], qkv[:, q_end:k_end], qkv[:, k_end:v_end], ctx.positions, self.num_heads,
             self.num_kv_heads, self.head_dim, self.value_dim, self.stored_dim, rotary=self.position,

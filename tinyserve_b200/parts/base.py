@@ -34,8 +34,8 @@ class ParamSpec:
     role "vector": small per-channel tensor; kept in the engine's dtype, but a
     tensor that the checkpoint stores in 32-bit stays 32-bit.
     role "int_table": integer table, kept as int32.
-    init: "normal" (N(0, 0.02)), "norm_weight" (1 + U(-0.1, 0.1)), "around_zero" (U(-0.1, 0.1)) or "zeros", used by
-    the random-weights mode.  ``sources`` lists the checkpoint tensors that fill it
+    init: "normal" (N(0, 0.02)), "norm_weight" (1 + U(-0.1, 0.1)), "around_zero" (U(-0.1, 0.1)), "wide" (N(0, 1)),
+    "unit_interval" (U(0.05, 0.95)) or "zeros", used by the random-weights mode.  ``sources`` lists the checkpoint tensors that fill it
     (default: one tensor of the same name and shape).  ``interleave_halves`` = b > 0: after the
     sources are placed, the rows of the first and the second half alternate in blocks of b rows
     (first-half rows [0, b), second-half rows [0, b), first-half rows [b, 2b), ...).
@@ -184,6 +184,13 @@ class Mixer(Part):
 
     def state_spec(self) -> Optional[StateSpec]:
         return None
+
+    def state_specs(self) -> dict:
+        """Every fixed-size per-request state of this mixer, by name; a run-order entry gets a state
+        entry for each (``BoundCall.state_of(name)``).  The one state of ``state_spec`` has the
+        name "" and is also ``BoundCall.state``."""
+        spec = self.state_spec()
+        return {} if spec is None else {"": spec}
 
     def work_tile_queries(self, dtype, page_size: int) -> int:
         """Queries per block of the attention work lists this mixer will ask for

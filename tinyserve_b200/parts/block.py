@@ -15,7 +15,7 @@ from __future__ import annotations
 
 from ..config.model_config import LayerSpec
 from ..kernels import ops
-from .base import Part, build_feed_forward, build_mixer, build_norm
+from .base import ParamSpec, Part, StateSpec, build_feed_forward, build_mixer, build_norm
 
 
 def add_and_norm(norm, x, residual, reader=None, rows=None, compute_dtype=None):
@@ -149,7 +149,74 @@ class SandwichBlock(Part):
         return ops.NormedAddend(self.ffn.forward(h, ctx), *self.ffn_out_norm.rms_parameters())
 
 
-ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock, "sandwich": SandwichBlock}
+class PostNormBlock(Part):
+    """The norm on the sub-layer's output only: r <- r + norm1(mixer(in1(r))), then
+    r <- r + norm2(ffn(in2(r))).  The sub-layers read the stream itself, through an input
+    convolution: in(r)_t = r_t + sum_j w[:, j] r_(t - taps + 1 + j), causal over time on every
+    channel (``LayerSpec.options["input_conv_taps"]``; the last taps - 1 rows of the stream are part
+    of a request's state, for each sub-layer of each block run).  The stream is 32-bit and every
+    output is added to it in 32-bit by the kernel that norms it; the block hands nothing on
+    unfinished.  A layer without a feed-forward (``LayerSpec.ffn`` None) has the first line only."""
+    capturable = True
+
+    def __init__(self, spec: LayerSpec, hidden_size: int):
+        super().__init__()
+        self.hidden_size = hidden_size
+        self.taps = int(spec.options.get("input_conv_taps", 0))
+        if not 1 <= self.taps <= ops.CAUSAL_CONV_MAX_TAPS:
+            raise ValueError(f"post-norm block: an input convolution of 1 to {ops.CAUSAL_CONV_MAX_TAPS} taps, got {self.taps}")
+        self.mixer = build_mixer(spec.mixer)
+        self.ffn = build_feed_forward(spec.ffn) if spec.ffn is not None else None
+        self.mixer_out_norm = build_norm(spec.norm, hidden_size)
+        self.ffn_out_norm = build_norm(spec.norm, hidden_size) if self.ffn is not None else None
+        for norm in (self.mixer_out_norm, self.ffn_out_norm):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise ValueError("post-norm block: its norms add their output to the stream themselves (group_rmsnorm)")
+        self._names = {"mixer": spec.name_of("mixer", self.mixer.tree_name),
+                       "ffn": spec.name_of("ffn", self.ffn.tree_name if self.ffn is not None else ""),
+                       "mixer_out_norm": spec.name_of("mixer_out_norm", "mixer_out_norm"),
+                       "ffn_out_norm": spec.name_of("ffn_out_norm", "ffn_out_norm"),
+                       "mixer_in_conv": spec.name_of("mixer_in_conv", "mixer_in_conv"),
+                       "ffn_in_conv": spec.name_of("ffn_in_conv", "ffn_in_conv")}
+
+    def children(self):
+        n = self._names
+        out = {n["mixer"]: self.mixer, n["mixer_out_norm"]: self.mixer_out_norm}
+        if self.ffn is not None:
+            out.update({n["ffn"]: self.ffn, n["ffn_out_norm"]: self.ffn_out_norm})
+        return out
+
+    def param_specs(self):
+        n = self._names
+        specs = {f"{n['mixer_in_conv']}.weight": ParamSpec((self.hidden_size, self.taps), init="around_zero")}
+        if self.ffn is not None:
+            specs[f"{n['ffn_in_conv']}.weight"] = ParamSpec((self.hidden_size, self.taps), init="around_zero")
+        return specs
+
+    def state_specs(self):
+        if self.taps < 2:
+            return {}
+        specs = {"mixer_in": StateSpec((self.taps - 1, self.hidden_size), "float32")}
+        if self.ffn is not None:
+            specs["ffn_in"] = StateSpec((self.taps - 1, self.hidden_size), "float32")
+        return specs
+
+    def _read(self, residual, which, ctx, call):
+        weight = self.w[f"{self._names[which + '_conv']}.weight"]
+        state = ctx.state(call.state_of(f"block.{which}")) if self.taps > 1 else None
+        return ops.causal_conv(residual, weight, state, ctx, ctx.dtype, add_input=True)
+
+    def forward(self, x, residual, ctx, call):
+        if x is not None:
+            raise ValueError("post-norm block: the block before it must leave the stream complete")
+        self.mixer_out_norm.add_normed(self.mixer.forward(self._read(residual, "mixer_in", ctx, call), ctx, call), residual)
+        if self.ffn is not None:
+            self.ffn_out_norm.add_normed(self.ffn.forward(self._read(residual, "ffn_in", ctx, call), ctx), residual)
+        return None
+
+
+ARRANGEMENTS = {"pre_norm": PreNormBlock, "parallel": ParallelBlock, "sandwich": SandwichBlock,
+                "post_norm": PostNormBlock}
 
 
 def build_block(spec: LayerSpec, hidden_size: int):

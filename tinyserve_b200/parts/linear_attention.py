@@ -16,7 +16,20 @@ the value size, silu gate, output projection) is ``MatrixStateMixer``; they diff
   factor; the heads of a token are normed together with one weight over all of them and multiplied
   by sigmoid (not silu) of the gate.
 
-Everything behind the projections is 32-bit (angles, decays, state, output norm):
+* ``HGRN2``: the forget gate also decides what is written: per key channel and token
+  f = l + (1 - l) sigmoid(W_f h + b) with a learned lower bound l, S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T
+  (no key), q = silu(W_q h), a weight of value size on the output norm, no gate.
+* ``MLSTM``: the matrix memory of xLSTM.  Per head and token a log input gate i and a log forget gate f,
+  both capped by cap tanh(. / cap), f through log-sigmoid; with the running maximum m_t = max(f_t + m_(t-1), i_t),
+  S_t = exp(f_t + m_(t-1) - m_t) S_(t-1) + exp(i_t - m_t) k_t v_t^T and n_t the same with k alone;
+  o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6), q times key_dim^(-1/2).  n rides in the state as a value
+  column of its own (the values get a column of ones); m is a second, small state.
+* ``Mamba2``: a selective state space in its state-space-duality form.  One input projection gives a gate z, values
+  x, per group B and C, and a step size per head; x, B, C pass a short causal convolution and silu;
+  dt = softplus(dt + bias), S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T, y_t = S_t^T C_t + D x_t;
+  y silu(z) is RMS-normed in groups over all heads.  B plays k, C plays q, shared by the heads of a group.
+
+Everything behind the projections is 32-bit (angles, decays, gates, step sizes, state, output norm):
 csrc/linear_attention.cu.  The decay logits z leave their product in 32-bit."""
 from __future__ import annotations
 
@@ -149,6 +162,165 @@ class Lightning(MatrixStateMixer):
         return ops.linear(out, self.w["o_proj.weight"], allow_pending=True)
 
 
+class HGRN2(Mixer):
+    tree_name = "mixer"
+    capturable = True
+
+    def __init__(self, hidden_size, num_heads, key_dim, value_dim, eps, names=None):
+        super().__init__()
+        self.names = dict({"q": "q", "f": "f", "v": "v", "o": "o", "lower": "lower", "norm": "norm"}, **(names or {}))
+        self.hidden_size, self.num_heads = hidden_size, num_heads
+        self.key_dim, self.value_dim, self.eps = key_dim, value_dim, float(eps)
+        if not ops.linear_attention_supports(key_dim) or not 0 < value_dim <= ops.LINEAR_ATTENTION_MAX_VALUE_DIM:
+            raise ValueError(f"hgrn2: key size {key_dim} or value size {value_dim} is not supported")
+        self.qk_size, self.v_size = num_heads * key_dim, num_heads * value_dim
+
+    def param_specs(self):
+        nm, qk, v, n = self.names, self.qk_size, self.v_size, self.hidden_size
+        return {
+            "in_proj.weight": ParamSpec((qk + v, n), sources=(Source(f"{nm['q']}.weight", 0, qk),
+                                                              Source(f"{nm['v']}.weight", qk, qk + v))),
+            "f_proj.weight": ParamSpec((qk, n), sources=(Source(f"{nm['f']}.weight", 0, qk),)),
+            "f_proj.bias": ParamSpec((qk,), role="vector", init="wide", sources=(Source(f"{nm['f']}.bias", 0, qk),)),
+            "lower": ParamSpec((qk,), role="vector", init="unit_interval", sources=(Source(nm["lower"], 0, qk),)),
+            "norm.weight": ParamSpec((self.value_dim,), role="vector", init="norm_weight",
+                                     sources=(Source(f"{nm['norm']}.weight", 0, self.value_dim),)),
+            "o_proj.weight": ParamSpec((n, v), sources=(Source(f"{nm['o']}.weight", 0, n),)),
+        }
+
+    def bind(self, tensors):
+        if "lower" in tensors:
+            tensors = dict(tensors, lower=tensors["lower"].float().contiguous())      # the bound enters a 32-bit gate
+        super().bind(tensors)
+
+    def state_spec(self):
+        return StateSpec((self.num_heads, self.key_dim, self.value_dim), "float32")
+
+    def forward(self, h, ctx, call):
+        proj = ops.materialize(ops.linear(h, self.w["in_proj.weight"]))
+        z = ops.linear(h, self.w["f_proj.weight"], self.w["f_proj.bias"], out_float32=True)
+        out = ops.linear_attention(proj[:, :self.qk_size], None, proj[:, self.qk_size:], None, ctx.state(call.state), ctx,
+                                   self.num_heads, self.key_dim, self.value_dim, ctx.dtype, decay_logits=z,
+                                   lower=self.w["lower"], tied_key=True, input_activation="q",
+                                   norm_weight=self.w["norm.weight"], eps=self.eps)
+        return ops.linear(out, self.w["o_proj.weight"], allow_pending=True)
+
+
+class MLSTM(Mixer):
+    tree_name = "mixer"
+    capturable = True
+
+    def __init__(self, hidden_size, num_heads, key_dim, value_dim, gate_cap, eps, names=None):
+        super().__init__()
+        self.names = dict({"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "i": "i", "f": "f", "norm": "norm"},
+                          **(names or {}))
+        self.hidden_size, self.num_heads = hidden_size, num_heads
+        self.key_dim, self.value_dim, self.eps, self.gate_cap = key_dim, value_dim, float(eps), float(gate_cap)
+        if not self.gate_cap > 0:
+            raise ValueError("mlstm: the gate cap must be positive")
+        # the state's value columns: the values, the normaliser's column of ones, zeros up to a multiple of four
+        self.state_cols = (value_dim // 4 + 1) * 4
+        if not ops.linear_attention_supports(key_dim) or not 0 < self.state_cols <= ops.LINEAR_ATTENTION_MAX_VALUE_DIM:
+            raise ValueError(f"mlstm: key size {key_dim} or value size {value_dim} is not supported")
+        self.qk_size, self.v_size = num_heads * key_dim, num_heads * value_dim
+
+    def param_specs(self):
+        nm, qk, v, n, H = self.names, self.qk_size, self.v_size, self.hidden_size, self.num_heads
+        rows, at = [], 0
+        for name, count in ((nm["q"], qk), (nm["k"], qk), (nm["v"], v), (nm["g"], v)):
+            rows.append(Source(f"{name}.weight", at, at + count))
+            at += count
+        return {
+            "in_proj.weight": ParamSpec((at, n), sources=tuple(rows)),
+            "gates.weight": ParamSpec((2 * H, n), sources=(Source(f"{nm['i']}.weight", 0, H), Source(f"{nm['f']}.weight", H, 2 * H))),
+            "gates.bias": ParamSpec((2 * H,), role="vector", init="wide",
+                                    sources=(Source(f"{nm['i']}.bias", 0, H), Source(f"{nm['f']}.bias", H, 2 * H))),
+            "norm.weight": ParamSpec((v,), role="vector", init="norm_weight", sources=(Source(f"{nm['norm']}.weight", 0, v),)),
+            "o_proj.weight": ParamSpec((n, v), sources=(Source(f"{nm['o']}.weight", 0, n),)),
+        }
+
+    def state_specs(self):
+        return {"": StateSpec((self.num_heads, self.key_dim, self.state_cols), "float32"),
+                "max": StateSpec((self.num_heads,), "float32")}
+
+    def forward(self, h, ctx, call):
+        proj = ops.materialize(ops.linear(h, self.w["in_proj.weight"]))
+        qk, v = self.qk_size, self.v_size
+        raw_gates = ops.linear(h, self.w["gates.weight"], self.w["gates.bias"], out_float32=True)
+        keep, write, floor = ops.mlstm_gates(raw_gates, self.gate_cap, ctx.state(call.state_of("max")), ctx, self.num_heads)
+        raw = ops.linear_attention(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + v], None, ctx.state(call.state),
+                                   ctx, self.num_heads, self.key_dim, self.state_cols, ctx.dtype, token_keep=keep,
+                                   token_write=write, q_scale=self.key_dim ** -0.5, value_width=self.value_dim, raw=True)
+        out = ops.mlstm_finish(raw, floor, self.w["norm.weight"], proj[:, 2 * qk + v:], self.eps, self.num_heads,
+                               self.value_dim, ctx.dtype)
+        return ops.linear(out, self.w["o_proj.weight"], allow_pending=True)
+
+
+class Mamba2(Mixer):
+    tree_name = "mixer"
+    capturable = True
+
+    def __init__(self, hidden_size, num_heads, value_dim, state_dim, groups, conv_taps, norm_groups, eps, names=None):
+        super().__init__()
+        self.names = dict({"in": "in", "conv": "conv", "dt_bias": "dt_bias", "a_log": "A_log", "skip": "D", "norm": "norm",
+                           "o": "o"}, **(names or {}))
+        self.hidden_size, self.num_heads, self.value_dim = hidden_size, int(num_heads), int(value_dim)
+        self.state_dim, self.groups, self.taps = int(state_dim), int(groups), int(conv_taps)
+        self.norm_groups, self.eps = int(norm_groups), float(eps)
+        self.inner = self.num_heads * self.value_dim
+        if self.groups < 1 or self.num_heads % self.groups:
+            raise ValueError(f"mamba2: {num_heads} heads do not split into {groups} groups")
+        if self.norm_groups < 1 or self.inner % self.norm_groups:
+            raise ValueError(f"mamba2: {self.inner} channels do not split into {norm_groups} norm groups")
+        if not 1 <= self.taps <= ops.CAUSAL_CONV_MAX_TAPS:
+            raise ValueError(f"mamba2: a convolution of 1 to {ops.CAUSAL_CONV_MAX_TAPS} taps, got {conv_taps}")
+        if not ops.linear_attention_supports(self.state_dim) or not 0 < self.value_dim <= ops.LINEAR_ATTENTION_MAX_VALUE_DIM:
+            raise ValueError(f"mamba2: state size {state_dim} or value size {value_dim} is not supported")
+        self.conv_channels = self.inner + 2 * self.groups * self.state_dim
+
+    def param_specs(self):
+        nm, n, H, C = self.names, self.hidden_size, self.num_heads, self.conv_channels
+        rows = self.inner + C + H
+        return {
+            "in_proj.weight": ParamSpec((rows, n), sources=(Source(f"{nm['in']}.weight", 0, rows),)),
+            "conv.weight": ParamSpec((C, self.taps), init="around_zero", sources=(Source(f"{nm['conv']}.weight", 0, C),)),
+            "conv.bias": ParamSpec((C,), role="matrix", init="normal", sources=(Source(f"{nm['conv']}.bias", 0, C),)),
+            "dt_bias": ParamSpec((H,), role="vector", init="wide", sources=(Source(nm["dt_bias"], 0, H),)),
+            "a_log": ParamSpec((H,), role="vector", init="wide", sources=(Source(nm["a_log"], 0, H),)),
+            "skip": ParamSpec((H,), role="vector", init="norm_weight", sources=(Source(nm["skip"], 0, H),)),
+            "norm.weight": ParamSpec((self.inner,), role="vector", init="norm_weight",
+                                     sources=(Source(f"{nm['norm']}.weight", 0, self.inner),)),
+            "o_proj.weight": ParamSpec((n, self.inner), sources=(Source(f"{nm['o']}.weight", 0, n),)),
+        }
+
+    def state_specs(self):
+        specs = {"": StateSpec((self.num_heads, self.state_dim, self.value_dim), "float32")}
+        if self.taps > 1:
+            specs["conv"] = StateSpec((self.taps - 1, self.conv_channels), "float32")
+        return specs
+
+    def forward(self, h, ctx, call):
+        inner, C, H, GN = self.inner, self.conv_channels, self.num_heads, self.groups * self.state_dim
+        weight = self.w["in_proj.weight"]
+        proj = ops.materialize(ops.linear(h, weight[:inner + C]))
+        # the step sizes enter the recurrence: their product leaves in 32-bit
+        dt_raw = ops.linear(h, weight[inner + C:], out_float32=True)
+        conv_state = ctx.state(call.state_of("conv")) if self.taps > 1 else None
+        xbc = ops.causal_conv(proj[:, inner:], self.w["conv.weight"], conv_state, ctx, ctx.dtype, bias=self.w["conv.bias"],
+                              activation="silu")
+        keep, write = ops.ssm_gates(dt_raw, self.w["dt_bias"], self.w["a_log"], H)
+        x = xbc[:, :inner]
+        raw = ops.linear_attention(xbc[:, inner + GN:], xbc[:, inner:inner + GN], x, None, ctx.state(call.state), ctx, H,
+                                   self.state_dim, self.value_dim, ctx.dtype, token_keep=keep, token_write=write,
+                                   qk_group=H // self.groups, raw=True)
+        out = ops.ssm_finish(raw, x, self.w["skip"], proj[:, :inner], self.w["norm.weight"], self.norm_groups, self.eps, H,
+                             self.value_dim, ctx.dtype)
+        return ops.linear(out, self.w["o_proj.weight"], allow_pending=True)
+
+
+register_mixer("hgrn2", HGRN2)
+register_mixer("mlstm", MLSTM)
+register_mixer("mamba2", Mamba2)
 register_mixer("retention", Retention)
 register_mixer("lightning", Lightning)
 register_mixer("gated_linear_attention", GatedLinearAttention)

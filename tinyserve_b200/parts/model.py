@@ -46,6 +46,28 @@ class BoundCall:
     state: int
     writes_cache: bool
     before: tuple = ()      # (stream operation, argument) pairs that run right before the block
+    # every state entry of the call, by name: ((name, index), ...).  A mixer's one state has the name
+    # ""; a mixer made of branches names a branch's states "<branch>" and "<branch>.<name>"; a block's
+    # own states (those of its ``state_specs``) start with "block."
+    states: tuple = ()
+
+    def state_of(self, name: str) -> int:
+        for key, index in self.states:
+            if key == name:
+                return index
+        raise KeyError(f"the call has no state {name!r}; it has {[k for k, _ in self.states]}")
+
+    def scoped(self, prefix: str) -> "BoundCall":
+        """The call as the part that lives under ``prefix`` sees it: its states without the prefix."""
+        states = tuple((key[len(prefix) + 1:] if key != prefix else "", index) for key, index in self.states
+                       if key == prefix or key.startswith(prefix + "."))
+        return BoundCall(self.layer, self.cache, _one_state(states), self.writes_cache, self.before, states)
+
+
+def _one_state(states) -> int:
+    """``BoundCall.state``: the mixer's state named "", or its only state, else -1."""
+    own = [(key, index) for key, index in states if not key.startswith("block.")]
+    return dict(own).get("", own[0][1] if len(own) == 1 else -1)
 
 
 @dataclass(frozen=True)
@@ -116,13 +138,17 @@ class DecoderModel(Part):
                     self.cache_entries.append(CacheEntryInfo(wspec, g, group_sizes[g]))
                     group_sizes[g] += 1
                 cache_index = cache_ids[call.cache]
-            sspec = mixer.state_spec()
-            state_index = -1
-            if sspec is not None:
-                state_index = len(self.state_entries)
+            named = dict(mixer.state_specs())
+            block_states = getattr(self.blocks[call.layer], "state_specs", None)
+            if block_states is not None:
+                named.update({f"block.{name}": sspec for name, sspec in block_states().items()})
+            states = []
+            for name, sspec in named.items():
+                states.append((name, len(self.state_entries)))
                 self.state_entries.append(sspec)
             before = tuple((self.stream_ops[name], arg) for name, arg in call.before)
-            self.calls.append(BoundCall(call.layer, cache_index, state_index, call.writes_cache, before))
+            self.calls.append(BoundCall(call.layer, cache_index, _one_state(states), call.writes_cache, before,
+                                        tuple(states)))
         self.group_sizes = group_sizes
 
     def named_parts(self):

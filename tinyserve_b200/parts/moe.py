@@ -9,7 +9,14 @@ side by side into one [hidden, E ff]: act(.) of an expert that a token did not c
 by zero, the others by their weight, and one product over K = E ff adds the chosen experts'
 outputs in 32-bit inside the product.  That is how a few tokens run (decoding: they touch most
 experts' weights anyway) and how the 32-bit engine runs; a bfloat16 step of many tokens sorts its
-rows by expert instead, so that an expert multiplies its own rows only (``ops.moe_grouped``)."""
+rows by expert instead, so that an expert multiplies its own rows only (``ops.moe_grouped``).
+
+Further forms, each a parameter.  ``activation`` "silu_gated": expert e is
+W_down,e (silu(W_gate,e h) * (W_up,e h)); its gate and up rows are stacked expert by expert
+[E 2 ff, hidden].  ``router`` "sigmoid_corrected": s = sigmoid(z); the choice is made on s + correction (a
+learned vector, ``correction``), the weights are s itself; with ``groups`` > 1 the experts form that
+many equal groups of neighbours, a group's score is the sum of its two largest choice scores, and
+only the experts of the ``keep_groups`` best groups can be chosen."""
 from __future__ import annotations
 
 import torch
@@ -17,7 +24,7 @@ import torch
 from ..kernels import ops
 from .base import FeedForward, ParamSpec, Source, register_feed_forward
 
-DEFAULT_NAMES = {"router": "router", "expert": "e{e}", "up": "up", "down": "down"}
+DEFAULT_NAMES = {"router": "router", "expert": "e{e}", "up": "up", "down": "down", "gate": "gate", "correction": "correction"}
 
 
 class MixtureOfExperts(FeedForward):
@@ -25,23 +32,44 @@ class MixtureOfExperts(FeedForward):
     capturable = True
     accepts_scaled_rows = False
 
-    def __init__(self, hidden_size, intermediate_size, num_experts, top, activation="relu_squared", names=None):
+    def __init__(self, hidden_size, intermediate_size, num_experts, top, activation="relu_squared", names=None,
+                 router="softmax", groups=1, keep_groups=1):
         super().__init__()
         self.names = dict(DEFAULT_NAMES, **(names or {}))
-        if activation != "relu_squared":
-            raise ValueError(f"mixture of experts: unknown activation {activation!r}; known: relu_squared")
+        if activation not in ("relu_squared", "silu_gated"):
+            raise ValueError(f"mixture of experts: unknown activation {activation!r}; known: relu_squared, silu_gated")
+        if router not in ("softmax", "sigmoid_corrected"):
+            raise ValueError(f"mixture of experts: unknown router {router!r}; known: softmax, sigmoid_corrected")
         if not 0 < top <= num_experts:
             raise ValueError(f"mixture of experts: {top} of {num_experts} experts")
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.num_experts, self.top = int(num_experts), int(top)
+        self.gated, self.router = activation == "silu_gated", router
+        self.groups, self.keep_groups = int(groups), int(keep_groups)
+        if self.groups < 1 or self.num_experts % self.groups or not 1 <= self.keep_groups <= self.groups:
+            raise ValueError(f"mixture of experts: {num_experts} experts in {groups} groups of which {keep_groups} are kept")
+        if (self.groups > 1 or self.keep_groups > 1) and router != "sigmoid_corrected":
+            raise ValueError("mixture of experts: groups of experts come with the sigmoid_corrected router")
+        if self.top > self.keep_groups * (self.num_experts // self.groups):
+            raise ValueError(f"mixture of experts: {top} experts cannot come from {keep_groups} groups of "
+                             f"{self.num_experts // self.groups}")
 
     def param_specs(self):
         nm, E, ff, n = self.names, self.num_experts, self.intermediate_size, self.hidden_size
         expert = lambda e: nm["expert"].format(e=e)
+        if self.gated:
+            up_sources = tuple(src for e in range(E) for src in (
+                Source(f"{expert(e)}.{nm['gate']}.weight", 2 * e * ff, (2 * e + 1) * ff),
+                Source(f"{expert(e)}.{nm['up']}.weight", (2 * e + 1) * ff, (2 * e + 2) * ff)))
+        else:
+            up_sources = tuple(Source(f"{expert(e)}.{nm['up']}.weight", e * ff, (e + 1) * ff) for e in range(E))
+        specs = {}
+        if self.router == "sigmoid_corrected":
+            specs["correction"] = ParamSpec((E,), role="vector", init="around_zero", sources=(Source(nm["correction"], 0, E),))
         return {
+            **specs,
             "router.weight": ParamSpec((E, n), sources=(Source(f"{nm['router']}.weight", 0, E),)),
-            "up.weight": ParamSpec((E * ff, n), sources=tuple(
-                Source(f"{expert(e)}.{nm['up']}.weight", e * ff, (e + 1) * ff) for e in range(E))),
+            "up.weight": ParamSpec((len(up_sources) * ff, n), sources=up_sources),
             # stored expert by expert [E hidden, ff]; ``bind`` lays them side by side
             "down.weight": ParamSpec((E * n, ff), sources=tuple(
                 Source(f"{expert(e)}.{nm['down']}.weight", e * n, (e + 1) * n) for e in range(E))),
@@ -49,20 +77,32 @@ class MixtureOfExperts(FeedForward):
 
     def bind(self, tensors):
         E, ff, n = self.num_experts, self.intermediate_size, self.hidden_size
+        tensors = dict(tensors)
+        if "correction" in tensors:
+            tensors["correction"] = tensors["correction"].float().contiguous()       # it joins 32-bit scores
         if "down.weight" in tensors:
             down = tensors["down.weight"]
-            tensors = dict(tensors)
             tensors["down.weight"] = down.view(E, n, ff).permute(1, 0, 2).reshape(n, E * ff).contiguous()
         super().bind(tensors)
+
+    def _route(self, logits):
+        if self.router == "sigmoid_corrected":
+            return ops.moe_route_scored(logits, self.w["correction"], self.top, self.groups, self.keep_groups)
+        return ops.moe_route(logits, self.top)
 
     def forward(self, h, ctx):
         logits = ops.linear(h, self.w["router.weight"], out_float32=True)
         if (h.dtype == torch.bfloat16 and self.top < self.num_experts and h.shape[0] >= ops.MOE_GROUPED_MIN_TOKENS
                 and self.hidden_size % 8 == 0 and self.intermediate_size % 8 == 0):
-            gates = ops.moe_route(logits, self.top)
-            return ops.moe_grouped(h, gates, self.w["up.weight"], self.w["down.weight"], self.top)
+            return ops.moe_grouped(h, self._route(logits), self.w["up.weight"], self.w["down.weight"], self.top,
+                                   gated=self.gated)
         a = ops.materialize(ops.linear(h, self.w["up.weight"]))
-        ops.moe_activate_(a, None, self.num_experts, logits=logits, top=self.top)      # (routes in the same kernel)
+        if self.gated:
+            a = ops.moe_gated_activate(a, self._route(logits), self.num_experts)
+        elif self.router == "softmax":
+            ops.moe_activate_(a, None, self.num_experts, logits=logits, top=self.top)      # (routes in the same kernel)
+        else:
+            ops.moe_activate_(a, self._route(logits), self.num_experts)
         return ops.linear(a, self.w["down.weight"], allow_pending=True)
 
 

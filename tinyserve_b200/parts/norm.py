@@ -75,3 +75,38 @@ class LayerNorm(Norm):
 
 
 register_norm("layernorm", LayerNorm)
+
+
+class GroupRMSNorm(Norm):
+    """RMS norm in groups: the row is cut into ``groups`` equal consecutive parts, each divided by
+    its own sqrt(mean(part^2) + eps), and the whole multiplied by the weight.  32-bit arithmetic;
+    one group is the plain RMS norm."""
+    capturable = True
+
+    def __init__(self, dim: int, eps: float, groups: int = 1):
+        super().__init__()
+        self.dim, self.eps, self.groups = dim, float(eps), int(groups)
+        if self.groups < 1 or dim % self.groups:
+            raise ValueError(f"group norm: {dim} columns do not split into {groups} equal groups")
+        self.compute_dtype = None
+
+    def prepare(self, runtime):
+        self.compute_dtype = runtime.dtype
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.dim,), role="vector", init="norm_weight")}
+
+    def forward(self, x, out=None):
+        return ops.group_norm(x, self.w["weight"], self.groups, self.eps, x.dtype)
+
+    def add_forward(self, x, residual, rows=None):
+        if x is not None:
+            raise ValueError("group norm: the stream it reads is complete (the block before adds its own outputs)")
+        return ops.group_norm(residual, self.w["weight"], self.groups, self.eps, self.compute_dtype, rows=rows)
+
+    def add_normed(self, y, residual):
+        """residual (float32, in place) += this norm of y."""
+        return ops.group_norm_add_(y, self.w["weight"], self.groups, self.eps, residual)
+
+
+register_norm("group_rmsnorm", GroupRMSNorm)

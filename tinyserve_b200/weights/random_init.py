@@ -25,6 +25,10 @@ def _draw(init: str, shape, generator, device="cpu"):
         return 1.0 + torch.empty(shape, dtype=torch.float32, device=device).uniform_(-0.1, 0.1, generator=generator)
     if init == "around_zero":
         return torch.empty(shape, dtype=torch.float32, device=device).uniform_(-0.1, 0.1, generator=generator)
+    if init == "wide":
+        return torch.empty(shape, dtype=torch.float32, device=device).normal_(0.0, 1.0, generator=generator)
+    if init == "unit_interval":
+        return torch.empty(shape, dtype=torch.float32, device=device).uniform_(0.05, 0.95, generator=generator)
     if init == "zeros":
         return torch.zeros(shape, dtype=torch.float32, device=device)
     raise ValueError(f"unknown init {init!r}")
