@@ -6,11 +6,20 @@ Notation: x [T, W] is the residual stream of one sequence, h the input of a sub-
 ``w`` a dict of the layer's tensors by checkpoint name without the layer prefix."""
 from __future__ import annotations
 
+import json
 import math
+import os
 
 import torch
 
 F64 = torch.float64
+
+
+def load_folder(folder):
+    from safetensors.torch import load_file
+    with open(os.path.join(folder, "config.json")) as fh:
+        cfg = json.load(fh)
+    return cfg, {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
 
 
 def rms(x, eps):
@@ -91,7 +100,7 @@ def alibi_slopes(H):
 
 def chunked_attention(h, w, cfg, eps):
     H, G, K, V = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"]
-    size, scale = cfg["mask"]["size"], float(cfg["scale"])
+    size, scale = (cfg.get("mask") or {}).get("size", 1 << 40), float(cfg["scale"])
     T = h.shape[0]
     q = rms(h @ w["q"].T + w["q.b"], eps) * w["q.norm"]
     k = rms(h @ w["k"].T + w["k.b"], eps) * w["k.norm"]
@@ -198,3 +207,19 @@ def forward(config, tensors, tokens, return_layers=False):
         layers.append(x.clone())
     logits = group_norm(x, t64["final.norm"], groups, eps) @ t64["head"].T
     return (logits, torch.stack(layers)) if return_layers else logits
+
+
+def logits(cfg, W, tokens):
+    return forward(cfg, W, tokens)
+
+
+def greedy(cfg, W, prompt, n):
+    """n greedy tokens after ``prompt``; with each, the gap between the best and the second logit."""
+    ids, out, gaps = list(prompt), [], []
+    for _ in range(n):
+        row = forward(cfg, W, ids)[-1]
+        best = torch.topk(row, 2)
+        out.append(int(best.indices[0]))
+        gaps.append(float(best.values[0] - best.values[1]))
+        ids.append(out[-1])
+    return out, gaps

@@ -872,6 +872,12 @@ def prefill_tile_queries(dtype, num_heads, num_kv_heads, head_dim, page_size=16)
 BIASED_ATTENTION_ON_TENSOR_CORES = False
 
 
+def biased_attention_backends(dtype, head_dim, page_size) -> list:
+    """The attention kernels that take a chunk mask and a distance bias at this head size, the one
+    the engine picks first."""
+    return ["simt"]
+
+
 def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None, backend=None, keep_first=0,
                     sinks=None, chunk=0, slopes=None):
     """Attention of this step's queries over their requests' cached keys and values.
