@@ -385,6 +385,28 @@ def delilorn_shapes(width):
     return delilorn, qwen3
 
 
+def tarivik_shapes(width):
+    """A Tarivik of real layer sizes at ``width``: attention in chunks of 1,024 beside a selective state
+    space, an HGRN2 layer, an mLSTM layer, and the three again: six blocks, each with 8 gated experts in
+    4 groups of which a token takes 2 from the best 2 groups, sized so that a token's active expert weights
+    equal those of the Delilorn beside it (same width, block count, attention heads, vocabulary)."""
+    delilorn, _ = delilorn_shapes(width)
+    heads, vocab = width // 128, 32768
+    ffe = (delilorn["layers"][0]["mlp"]["expert"]["ff"] * 2 // 3 + 63) // 64 * 64      # three matrices where Delilorn has two
+    moe = {"kind": "moe", "expert": {"ff": ffe}, "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    parallel = {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                         "mask": {"size": 1024}},
+                "right": {"heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1},
+                "left_scale": 1.0, "right_scale": 1.0}
+    hgrn2 = {"heads": heads // 2, "dim": 128, "vdim": 256}
+    mlstm = {"heads": heads, "dim": 128, "vdim": 128, "gate_cap": 15.0}
+    layer = lambda kind, mixer: {"type": kind, "mixer": mixer, "mlp": moe}
+    order = [layer("parallel", parallel), layer("hgrn2", hgrn2), layer("mlstm", mlstm)]
+    tarivik = {"architecture": "Tarivik", "vocab": vocab, "width": width, "max_positions": CONTEXT, "norm": {"eps": 1e-6, "groups": 2},
+               "canon": {"taps": 4}, "layers": order + order}
+    return tarivik, delilorn
+
+
 def _time_us(fn, iters=20):
     import torch
     for _ in range(3):
@@ -576,11 +598,153 @@ def delilorn_kernel_table(width, peaks):
     return out
 
 
-ARCH_BENCHES = {"dudatar": (dudatar_shapes, kernel_table), "delilorn": (delilorn_shapes, delilorn_kernel_table)}
+def tarivik_kernel_table(width, peaks):
+    """Tarivik's kernels beside the like kernels of Delilorn at this width, time over roofline time:
+    attention in chunks with a distance bias and a sink beside attention over a window with kept tokens (the
+    FLOPs and bytes of the visible keys only); the HGRN2, mLSTM (gates, scan, finish) and state-space
+    (convolution, step sizes, scan, finish) forms of the matrix-state scan beside the lightning form; the
+    gated experts beside Delilorn's; the output norm added to the stream plus the next input convolution
+    beside the norm that norms a sub-layer's output, adds it and norms the sum."""
+    import torch
+    from types import SimpleNamespace
+    from tinyserve_b200.engine.batch import GroupView, StepContext
+    from tinyserve_b200.kernels import ops
+    from tinyserve_b200.parts.moe import MixtureOfExperts
+    dev, bf = "cuda:0", torch.bfloat16
+    raw, other = tarivik_shapes(width)
+    par, hg, ml = (raw["layers"][i]["mixer"] for i in (0, 1, 2))
+    left, right = par["left"], par["right"]
+    lig, win = other["layers"][1]["mixer"], other["layers"][3]["mixer"]
+    fma_tflops = ops.num_sms() * 128 * 2 * 1.965e9 / 1e12
+    out = {}
+
+    def frac(key, us, roof):
+        out[key] = {"us": round(us, 1), "roofline_us": round(roof, 2), "frac": round(roof / us, 3)}
+
+    for name, lengths, starts in (("prefill_2048", [2048], [0]), ("decode_b8", [1] * 8, [2048] * 8)):
+        T, B = sum(lengths), len(lengths)
+        kv_len, page = starts[0] + lengths[0], 64
+        pages_per = -(-kv_len // page)
+        cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=dev)
+        table = (torch.arange(B * pages_per, dtype=torch.int32, device=dev) + 1).view(B, pages_per)
+        pos = torch.arange(kv_len - lengths[0], kv_len)
+
+        def attention(H, G, D, seen, **kw):
+            kc = torch.randn(B * pages_per + 1, G, page, D, device=dev).to(bf)
+            vc = torch.randn_like(kc)
+            view = GroupView(page, pages_per, None, table, kc.shape[0])
+            q = torch.randn(T, H, D, device=dev).to(bf)
+            sc = StepContext()
+            sc.num_tokens, sc.num_requests, sc.max_q_len, sc.max_kv_len = T, B, max(lengths), kv_len
+            sc.cu_q, sc.kv_lens = cu, torch.full((B,), kv_len, dtype=torch.int32, device=dev)
+            sc.host = {"cu_q": cu.tolist(), "kv_lens": [kv_len] * B}
+            us = _time_us(lambda: ops.paged_attention(q, kc, vc, view, sc, D ** -0.5, **kw))
+            roof = (4.0 * H * D * seen / (peaks["bf16_tflops"] * 1e6) if T > B
+                    else B * seen * 2 * G * D * 2 / (peaks["hbm_gbs"] * 1e3))
+            return us, roof
+
+        H, G, chunk = left["heads"], left["kv_heads"], left["mask"]["size"]
+        slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device=dev)
+        frac(f"chunked_attention_{name}", *attention(H, G, 128, float((pos % chunk + 1).sum()), chunk=chunk, slopes=slopes,
+                                                     sinks=torch.randn(H, device=dev)))
+        window, keep = win["mask"]["size"], win["mask"]["keep_first"]
+        seen = torch.minimum(pos + 1, torch.full_like(pos, window)) + torch.clamp(
+            torch.minimum(pos + 1 - window, torch.full_like(pos, keep)), min=0)
+        frac(f"delilorn_window_attention_{name}", *attention(H, G, 128, float(seen.sum()), window=window, keep_first=keep))
+        # the scans
+        ctx = SimpleNamespace(num_requests=B, cu_q=cu, max_q_len=max(lengths),
+                              state_slots=torch.arange(B, dtype=torch.int32, device=dev),
+                              fresh=torch.zeros(B, dtype=torch.int32, device=dev),
+                              positions=torch.cat([torch.arange(s, s + m) for s, m in zip(starts, lengths)]).int().to(dev))
+
+        def scan_roof(heads, n, nv, row_bytes):
+            return max((T * row_bytes + 2 * B * heads * n * nv * 4) / (peaks["hbm_gbs"] * 1e3),
+                       4.0 * T * heads * n * nv / (fma_tflops * 1e6))
+
+        Hh, n, nv = hg["heads"], hg["dim"], hg["vdim"]
+        proj = torch.randn(T, Hh * n + Hh * nv, device=dev).to(bf)
+        z, low = torch.randn(T, Hh * n, device=dev) + 3, torch.rand(Hh * n, device=dev)
+        state, wv = torch.zeros(B, Hh, n, nv, device=dev), torch.ones(nv, device=dev, dtype=bf)
+        frac(f"hgrn2_scan_{name}", _time_us(lambda: ops.linear_attention(
+            proj[:, :Hh * n], None, proj[:, Hh * n:], None, state, ctx, Hh, n, nv, bf, decay_logits=z, lower=low, tied_key=True,
+            input_activation="q", norm_weight=wv, eps=1e-6)), scan_roof(Hh, n, nv, (Hh * n + 2 * Hh * nv) * 2 + Hh * n * 4))
+        Hm, n, nv = ml["heads"], ml["dim"], ml["vdim"]
+        cols = (nv // 4 + 1) * 4
+        proj = torch.randn(T, 2 * Hm * n + 2 * Hm * nv, device=dev).to(bf)
+        gates_raw, m_state = torch.randn(T, 2 * Hm, device=dev), torch.zeros(B, Hm, device=dev)
+        state, wn = torch.zeros(B, Hm, n, cols, device=dev), torch.ones(Hm * nv, device=dev, dtype=bf)
+
+        def mlstm():
+            keep_, write, floor = ops.mlstm_gates(gates_raw, 15.0, m_state, ctx, Hm)
+            o = ops.linear_attention(proj[:, :Hm * n], proj[:, Hm * n:2 * Hm * n], proj[:, 2 * Hm * n:2 * Hm * n + Hm * nv], None,
+                                     state, ctx, Hm, n, cols, bf, token_keep=keep_, token_write=write, q_scale=n ** -0.5,
+                                     value_width=nv, raw=True)
+            return ops.mlstm_finish(o, floor, wn, proj[:, 2 * Hm * n + Hm * nv:], 1e-6, Hm, nv, bf)
+        frac(f"mlstm_gates_scan_finish_{name}", _time_us(mlstm), scan_roof(Hm, n, nv, (2 * Hm * n + 3 * Hm * nv) * 2))
+        Hs, nv, n, taps = right["heads"], right["vdim"], right["state"], right["conv"]
+        inner, C = Hs * nv, Hs * nv + 2 * right["groups"] * n
+        proj = torch.randn(T, inner + C, device=dev).to(bf)
+        dt_raw, conv_state = torch.randn(T, Hs, device=dev), torch.zeros(B, taps - 1, C, device=dev)
+        cw, cb = (torch.randn(C, taps, device=dev) * 0.3).to(bf), torch.zeros(C, device=dev, dtype=bf)
+        dtb, alog, skip = (torch.zeros(Hs, device=dev, dtype=bf) for _ in range(3))
+        state, wn = torch.zeros(B, Hs, n, nv, device=dev), torch.ones(inner, device=dev, dtype=bf)
+
+        def ssm():
+            xbc = ops.causal_conv(proj[:, inner:], cw, conv_state, ctx, bf, bias=cb, activation="silu")
+            keep_, write = ops.ssm_gates(dt_raw, dtb, alog, Hs)
+            o = ops.linear_attention(xbc[:, inner + n * right["groups"]:], xbc[:, inner:inner + n * right["groups"]], xbc[:, :inner],
+                                     None, state, ctx, Hs, n, nv, bf, token_keep=keep_, token_write=write,
+                                     qk_group=Hs // right["groups"], raw=True)
+            return ops.ssm_finish(o, xbc[:, :inner], skip, proj[:, :inner], wn, right["norm_groups"], 1e-6, Hs, nv, bf)
+        frac(f"state_space_conv_scan_finish_{name}", _time_us(ssm), scan_roof(Hs, n, nv, (2 * inner + C) * 2))
+        Hl, n, nv = lig["heads"], lig["dim"], lig["vdim"]
+        proj = torch.randn(T, 2 * Hl * n + 2 * Hl * nv, device=dev).to(bf)
+        state, wj = torch.zeros(B, Hl, n, nv, device=dev), torch.ones(Hl * nv, device=dev)
+        decay = torch.full((Hl,), 0.99, device=dev)
+        frac(f"delilorn_lightning_scan_{name}", _time_us(lambda: ops.linear_attention(
+            proj[:, :Hl * n], proj[:, Hl * n:2 * Hl * n], proj[:, 2 * Hl * n:2 * Hl * n + Hl * nv], proj[:, 2 * Hl * n + Hl * nv:],
+            state, ctx, Hl, n, nv, bf, decay=decay, norm_weight=wj, eps=1e-6, input_activation="silu", gate_activation="sigmoid",
+            joint_norm=True)), scan_roof(Hl, n, nv, (2 * Hl * n + 3 * Hl * nv) * 2))
+        # the experts of both designs (equal active weights)
+        h = torch.randn(T, width, device=dev).to(bf)
+        for key, cfg, kw in (("gated_experts", raw["layers"][0]["mlp"], dict(activation="silu_gated", router="sigmoid_corrected",
+                                                                           groups=4, keep_groups=2)),
+                             ("delilorn_experts", other["layers"][0]["mlp"], {})):
+            E, top, ffe = cfg["router"]["experts"], cfg["router"]["top"], cfg["expert"]["ff"]
+            mats = 3 if kw else 2
+            part = MixtureOfExperts(width, ffe, E, top, **kw)
+            tensors = {"router.weight": (torch.randn(E, width, device=dev) * 0.1).to(bf),
+                       "up.weight": (torch.randn(E * ffe * (mats - 1), width, device=dev) * 0.02).to(bf),
+                       "down.weight": (torch.randn(E * width, ffe, device=dev) * 0.02).to(bf)}
+            if kw:
+                tensors["correction"] = torch.zeros(E, device=dev)
+            part.bind(tensors)
+            us = _time_us(lambda: ops.materialize(part.forward(h, None)))
+            frac(f"{key}_{name}", us, 2.0 * mats * T * top * width * ffe / (peaks["bf16_tflops"] * 1e6) if T > B
+                 else mats * E * width * ffe * 2 / (peaks["hbm_gbs"] * 1e3))
+        # what stands between two sub-layers
+        res = torch.randn(T, width, device=dev)
+        y = torch.randn(T, width, device=dev).to(bf)
+        wn, wf = torch.ones(width, device=dev, dtype=bf), torch.ones(width, device=dev)
+        cw, cstate = (torch.randn(width, 4, device=dev) * 0.1).to(bf), torch.zeros(B, 3, width, device=dev)
+
+        def between():
+            ops.group_norm_add_(y, wn, 2, 1e-6, res)
+            return ops.causal_conv(res, cw, cstate, ctx, bf, add_input=True)
+        frac(f"group_norm_add_and_input_conv_{name}", _time_us(between), T * width * (8 + 2 + 4 + 2) / (peaks["hbm_gbs"] * 1e3))
+        frac(f"delilorn_normed_add_rmsnorm_{name}", _time_us(lambda: ops.normed_add_rmsnorm(ops.NormedAddend(y, wf, 1e-6), res, wf, 1e-6, bf)),
+             T * width * (8 + 2 + 2) / (peaks["hbm_gbs"] * 1e3))
+    return out
+
+
+# design -> (its shapes and those of the model beside it, its kernel table, the name of the model beside it)
+ARCH_BENCHES = {"dudatar": (dudatar_shapes, kernel_table, "qwen3"), "delilorn": (delilorn_shapes, delilorn_kernel_table, "qwen3"),
+                "tarivik": (tarivik_shapes, tarivik_kernel_table, "delilorn")}
 
 
 def arch_main(a) -> int:
-    """``--arch dudatar`` / ``--arch delilorn``: the design beside Qwen3 at equal size.  One JSON line."""
+    """``--arch dudatar`` / ``--arch delilorn``: the design beside Qwen3 at equal size; ``--arch tarivik``: beside
+    Delilorn, the closest design (experts, matrix-state mixers, attention with a sink).  One JSON line."""
     import torch
     from tinyserve_b200 import LLM
     from tinyserve_b200.config import config_from_dict
@@ -589,8 +753,8 @@ def arch_main(a) -> int:
     sizes = {}
     for width in [int(w) for w in a.sizes.split(",")]:
         entry = {}
-        shapes, table = ARCH_BENCHES[a.arch]
-        for name, raw in zip((a.arch, "qwen3"), shapes(width)):
+        shapes, table, beside = ARCH_BENCHES[a.arch]
+        for name, raw in zip((a.arch, beside), shapes(width)):
             llm = LLM(model_config=config_from_dict(raw), random_weights=True, dtype="bfloat16", max_model_len=CONTEXT,
                       block_size=a.block_size, max_num_seqs=8, max_num_batched_tokens=PREFILL_TOKENS,
                       num_blocks=8 * (CONTEXT // a.block_size) // 2 + 4096 // a.block_size, use_cuda_graphs=False, seed=a.seed)
@@ -605,7 +769,8 @@ def arch_main(a) -> int:
             llm = None
         entry["kernels"] = table(width, peaks)
         sizes[str(width)] = entry
-    print(json.dumps({"metric": f"prefill and decode tok/s, {a.arch.capitalize()} beside Qwen3 at equal size (random weights)",
+    beside = ARCH_BENCHES[a.arch][2].capitalize()
+    print(json.dumps({"metric": f"prefill and decode tok/s, {a.arch.capitalize()} beside {beside} at equal size (random weights)",
                       "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "steps": steps,
                       "warmup": warmup, "block_runs": 6, "sizes": sizes, "peaks": peaks}))
     return 0
@@ -649,9 +814,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the 0.6B burst, the 32B run and the long-context decode")
-    ap.add_argument("--arch", choices=["qwen3", "dudatar", "delilorn"], default="qwen3",
-                    help="dudatar, delilorn: measure that design beside Qwen3 at equal size instead of the default workload")
-    ap.add_argument("--sizes", default="2048,4096", help="--arch dudatar / delilorn: model widths to measure")
+    ap.add_argument("--arch", choices=["qwen3", "dudatar", "delilorn", "tarivik"], default="qwen3",
+                    help="dudatar, delilorn: measure that design beside Qwen3 at equal size instead of the default workload; "
+                         "tarivik: beside Delilorn")
+    ap.add_argument("--sizes", default="2048,4096", help="--arch dudatar / delilorn / tarivik: model widths to measure")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_main(a)
