@@ -16,6 +16,8 @@
 // window W > 0, j > p - W or j < keep_first (the first keys of a sequence may stay visible to all
 // later queries: the walk over the key tiles then starts with the tiles that hold them).  With
 // `sinks`, head h's softmax sum holds one more term exp(sinks[h]) that has no key and no value.
+// With `chunk` C > 0 (and no window) key j is seen iff j <= p and j / C == p / C, chunks counted from
+// position 0 of the sequence; with `slopes`, head h's scaled score of (p, j) loses slopes[h] * (p - j).
 // Keys are found through the block table; the cache layout is [page, kv_head, slot, head_dim].
 #include "tcgen05.cuh"
 
@@ -60,6 +62,8 @@ struct MmaAttnParams {
   int num_splits, window;
   int keep_first;           // with a window: keys below this stay visible
   const float* sinks;       // [H] or null
+  int chunk;                // > 0: a query at position i sees key j only if i / chunk == j / chunk (no window then)
+  const float* slopes;      // [H] or null: slopes[h] * (i - j) is taken off head h's scaled score
   float scale_log2;
   // Decode straight from the fused q/k/v projection (from_qkv != 0; q is not read): every block
   // builds its query rows itself (sum of the split-K partial tiles, per-head RMSNorm, rotary), and
@@ -194,10 +198,12 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[N
 // pos[h] is the position of row h's query, lo[h] the lowest visible key of its window (keys below
 // `keep` are visible besides); a row with pos < 0 sees nothing.
 // MASK false: every key of the tile is visible to both rows (no comparisons).
-template <int NT, bool MASK = true>
+// BIAS: row h's score of key j loses sl[h] * (pos[h] - j) (sl in the log2 domain, like the scale).
+template <int NT, bool MASK = true, bool BIAS = false>
 __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[D / 8][4], float (&m)[2],
                                              float (&l)[2], const int (&pos)[2], const int (&lo)[2],
-                                             int jbase, float scale_log2, int lane, int keep = 0) {
+                                             int jbase, float scale_log2, int lane, int keep = 0,
+                                             const float* sl = nullptr) {
   const int t = lane & 3;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -208,7 +214,8 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[D / 8
       for (int e = 0; e < 2; ++e) {
         const int j = jbase + nt * 8 + 2 * t + e;
         const bool visible = !MASK || (j <= pos[h] && (j >= lo[h] || j < keep));
-        const float v = visible ? s[nt][2 * h + e] * scale_log2 : -INFINITY;
+        const float v = !visible ? -INFINITY
+                        : (BIAS ? fmaf(s[nt][2 * h + e], scale_log2, sl[h] * (float)(j - pos[h])) : s[nt][2 * h + e] * scale_log2);
         s[nt][2 * h + e] = v;
         mx = fmaxf(mx, v);
       }
@@ -269,7 +276,7 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams
     cp_async16(smem_u32(Qs + r * ROW_BYTES + c * 16), src, valid);
   }
   const int j_hi = min(kv_len, pos0 + nq);
-  const int j_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int j_lo = p.chunk > 0 ? pos0 / p.chunk * p.chunk : (p.window > 0 ? max(0, pos0 - p.window + 1) : 0);
   const int first_tile = j_lo / BN, end_tile = (j_hi + BN - 1) / BN;
   // the walk: the tiles of the kept first keys that lie before the window's first tile, then the window's
   const int keep = p.window > 0 ? min(p.keep_first, j_hi) : 0;
@@ -280,12 +287,14 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams
   cp_async_commit();
 
   int pos[2], lo[2];
+  float sl[2];
   int warp_max_pos = -1, warp_min_pos = -1, warp_max_lo = 0;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp * 16 + g + 8 * h;
     pos[h] = r < n_valid ? pos0 + (QPT > 1 ? r / GT : 0) : -1;
-    lo[h] = p.window > 0 ? max(0, pos[h] - p.window + 1) : 0;
+    lo[h] = p.chunk > 0 ? max(0, pos[h]) / p.chunk * p.chunk : (p.window > 0 ? max(0, pos[h] - p.window + 1) : 0);
+    sl[h] = p.slopes && r < n_valid ? p.slopes[kvh * G + g0 + (QPT > 1 ? r % GT : r)] * LOG2E : 0.f;
   }
   {
     const int last = min(warp * 16 + 15, n_valid - 1);
@@ -293,7 +302,7 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams
       warp_max_pos = pos0 + (QPT > 1 ? last / GT : 0);
       // a tile needs no mask if all 16 rows of the warp are valid and see all of its keys
       if (last == warp * 16 + 15) warp_min_pos = pos0 + (QPT > 1 ? (warp * 16) / GT : 0);
-      warp_max_lo = p.window > 0 ? max(0, warp_max_pos - p.window + 1) : 0;
+      warp_max_lo = p.chunk > 0 ? warp_max_pos / p.chunk * p.chunk : (p.window > 0 ? max(0, warp_max_pos - p.window + 1) : 0);
     }
   }
   float o[D / 8][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -326,10 +335,15 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
       qk_tile<BN / 8>(s, my_q, qf, Ks + buf * BN * ROW_BYTES, 0, lane);
-      if (tile * BN + BN - 1 <= warp_min_pos && (tile * BN >= warp_max_lo || tile * BN + BN <= keep))
+      const bool open = tile * BN + BN - 1 <= warp_min_pos && (tile * BN >= warp_max_lo || tile * BN + BN <= keep);
+      if (p.slopes) {
+        if (open) softmax_tile<BN / 8, false, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane, 0, sl);
+        else softmax_tile<BN / 8, true, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane, keep, sl);
+      } else if (open) {
         softmax_tile<BN / 8, false>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane);
-      else
+      } else {
         softmax_tile<BN / 8, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane, keep);
+      }
       pv_tile<BN / 8>(o, s, Vs + buf * BN * ROW_BYTES, 0, lane);
     }
     __syncthreads();
@@ -515,7 +529,8 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
   const int* bt = p.block_table + (size_t)b * p.max_blocks;
   const int qpos = kv_len - 1;
-  const int j_hi = kv_len, j_lo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
+  const int j_hi = kv_len;
+  const int j_lo = p.chunk > 0 ? max(0, qpos) / p.chunk * p.chunk : (p.window > 0 ? max(0, qpos - p.window + 1) : 0);
   // the walk over the key tiles: the tiles of the kept first keys that lie before the window's first
   // tile, then the window's; the key ranges cut the walk
   const int keep = p.window > 0 ? min(p.keep_first, j_hi) : 0;
@@ -625,10 +640,12 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
   }
   if (traced) timeline_mark_thread(43, split);          // query rows (and the newest key) made
   int pos[2], lo[2];
+  float sl[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     pos[h] = g + 8 * h < ng ? qpos : -1;
     lo[h] = j_lo;
+    sl[h] = p.slopes && g + 8 * h < ng ? p.slopes[kvh * G + g0 + g + 8 * h] * LOG2E : 0.f;
   }
   float o[D / 8][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
@@ -672,7 +689,8 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
     if (jbase < j_hi) {
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       qk_tile<2, TMA>(s, Qs, qf, Ks + buf * KV_TILE, warp * 16, lane);
-      softmax_tile<2>(s, o, m, l, pos, lo, jbase, p.scale_log2, lane, keep);
+      if (p.slopes) softmax_tile<2, true, true>(s, o, m, l, pos, lo, jbase, p.scale_log2, lane, keep, sl);
+      else softmax_tile<2>(s, o, m, l, pos, lo, jbase, p.scale_log2, lane, keep);
       pv_tile<2, TMA>(o, s, Vs + buf * KV_TILE, warp * 16, lane);
     }
     __syncthreads();
@@ -858,11 +876,14 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
                                      int num_splits, float* part_o, float* part_ml,
                                      int decode_only, const int* tile_req, const int* tile_q0, int num_tiles,
                                      int tile_queries, int num_pages, int keep_first, const float* sinks,
-                                     cudaStream_t stream) {
+                                     int chunk, const float* slopes, cudaStream_t stream) {
   TS_REQUIRE(keep_first >= 0, "paged_attention_mma: keep_first %d", keep_first);
+  TS_REQUIRE(chunk >= 0 && (chunk == 0 || window <= 0), "paged_attention_mma: a chunk of %d positions (and no window beside it)", chunk);
   MmaAttnParams extra = {};
   extra.keep_first = keep_first;
   extra.sinks = sinks;
+  extra.chunk = chunk;
+  extra.slopes = slopes;
   return paged_attention_mma_impl(&extra, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
                                   num_requests, max_q_len, H, Hkv, page_size, max_blocks, scale, window, num_splits,
                                   part_o, part_ml, decode_only, tile_req, tile_q0, num_tiles,

@@ -22,7 +22,8 @@
 //            is the first one;
 //   warps 2-5 (tile 0) and 6-9 (tile 1), one thread per row: read the row of S from tensor memory,
 //            mask (key j is visible to the query at position p iff j <= p and, with a window
-//            W > 0, j > p - W: serve.py:668-680), online softmax in 32-bit with exp2
+//            W > 0, j > p - W: serve.py:668-680; with a chunk C > 0, j / C == p / C; with slopes, head
+//            h's scaled score loses slopes[h] * (p - j)), online softmax in 32-bit with exp2
 //            (tinykernels.py:386-413, 993), write P as bfloat16 over the first columns of S_g,
 //            rescale the row of O when its maximum moved; at the end divide O by the row sum and
 //            store it.
@@ -74,6 +75,8 @@ struct TcAttnParams {
   int window;
   int keep_first;           // with a window: keys below this stay visible (their tiles come first in the walk)
   const float* sinks;       // [H] or null: one more term exp(sinks[h]) in every softmax sum of head h
+  int chunk;                // > 0: a query at position i sees key j only if i / chunk == j / chunk (no window then)
+  const float* slopes;      // [H] or null: slopes[h] * (i - j) is taken off head h's scaled score
   float scale_log2;
 };
 
@@ -162,7 +165,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int groups = nq_all > QPT ? 2 : 1;       // query tiles of this block that hold queries
   const int pos0 = kv_len - q_len + q0;
   const int j_hi = min(kv_len, pos0 + nq_all);
-  const int j_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int j_lo = p.chunk > 0 ? pos0 / p.chunk * p.chunk : (p.window > 0 ? max(0, pos0 - p.window + 1) : 0);
   const int first_tile = j_lo / BN, end_tile = (j_hi + BN - 1) / BN;
   // the walk over the key tiles: those of the kept first keys that lie before the window's first tile, then the window's
   const int keep = p.window > 0 ? min(p.keep_first, j_hi) : 0;
@@ -305,7 +308,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const bool valid = r < n_valid;
       const int qi = QPT > 1 ? r / GT : 0, gg = QPT > 1 ? r % GT : r;
       const int pos = valid ? kv_len - q_len + qg + qi : -1;
-      const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+      const int lo = p.chunk > 0 ? max(0, pos) / p.chunk * p.chunk : (p.window > 0 ? max(0, pos - p.window + 1) : 0);
+      // the distance bias in the log2 domain, like the scale: the score of key j loses slope2 * (pos - j)
+      const bool biased = p.slopes != nullptr;
+      const float slope2 = biased && valid ? p.slopes[kvh * G + g0 + gg] * 1.4426950408889634f : 0.f;
       const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
       const uint32_t tmem_s = tmem_base + g * BN, tmem_o = tmem_base + 2 * BN + g * 128;
       const bool tracer = traced && (threadIdx.x & 127) == 64;
@@ -337,6 +343,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int c = 0; c < BN; c += 32) tmem_load32_nowait(tmem_s + lane_addr + c, sv + c);
         tmem_load_wait();
         if (tracer) timeline_mark_thread(21 + 4 * g, t);
+        float sc = p.scale_log2;
+        if (biased) {
+          // scaled and biased here, so that the maximum below is the biased scores'; the scale is spent
+          const float base = slope2 * (float)(j0 - pos);
+#pragma unroll
+          for (int e = 0; e < BN; ++e) sv[e] = fmaf(sv[e], p.scale_log2, fmaf(slope2, (float)e, base));
+          sc = 1.f;
+        }
         if (!all_visible) {
 #pragma unroll
           for (int e = 0; e < BN; ++e) {
@@ -358,7 +372,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // until then the probabilities are taken against the old reference (at most 256, exact
         // enough in bfloat16 and harmless in the 32-bit sums) and O needs no rescaling; the final
         // division by the row sum, kept against the same reference, gives the same result.
-        const float m_cand = fmaxf(m, mx * p.scale_log2);
+        const float m_cand = fmaxf(m, mx * sc);
         const float m_new = (m_cand - m <= 8.f) ? m : m_cand;      // -inf - -inf: moves (to -inf), harmless
         const float m_safe = m_new == -INFINITY ? 0.f : m_new;
         const float alpha = ex2(m - m_safe);
@@ -372,8 +386,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           float packed[32];
 #pragma unroll
           for (int e = 0; e < 64; e += 2) {
-            const float p0 = ex2(fmaf(sv[c + e], p.scale_log2, -m_safe));        // -inf gives 0
-            const float p1 = ex2(fmaf(sv[c + e + 1], p.scale_log2, -m_safe));
+            const float p0 = ex2(fmaf(sv[c + e], sc, -m_safe));        // -inf gives 0
+            const float p1 = ex2(fmaf(sv[c + e + 1], sc, -m_safe));
             sum4[(e / 2) & 3] += p0 + p1;
             packed[e / 2] = __uint_as_float(pack2(p0, p1));
           }
@@ -478,8 +492,10 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
                                          int num_tokens, int num_requests, int max_q_len, int H, int Hkv,
                                          int num_pages, int page_size, int max_blocks, float scale, int window,
                                          const int* tile_req, const int* tile_q0, int num_tiles,
-                                         int tile_queries, int keep_first, const float* sinks, cudaStream_t stream) {
+                                         int tile_queries, int keep_first, const float* sinks, int chunk,
+                                         const float* slopes, cudaStream_t stream) {
   TS_REQUIRE(keep_first >= 0, "paged_attention_tcgen05: keep_first %d", keep_first);
+  TS_REQUIRE(chunk >= 0 && (chunk == 0 || window <= 0), "paged_attention_tcgen05: a chunk of %d positions (and no window beside it)", chunk);
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_tcgen05: empty batch");
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_tcgen05: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size >= 8 && page_size <= BN && (page_size & (page_size - 1)) == 0,
@@ -493,6 +509,7 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
   p.tile_req = tile_req; p.tile_q0 = tile_q0;
   p.H = H; p.Hkv = Hkv; p.page_size = page_size; p.max_blocks = max_blocks; p.window = window;
   p.keep_first = keep_first; p.sinks = sinks;
+  p.chunk = chunk; p.slopes = slopes;
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.scale_log2 = scale * 1.4426950408889634f;

@@ -91,11 +91,17 @@ def bench_attention(a):
     ctx = SimpleNamespace(cu_q=cu, kv_lens=kv, num_requests=B, max_q_len=q_len, max_kv_len=kv_len,
                           host={"cu_q": cu.tolist(), "kv_lens": kv.tolist()}, tile_cache={})
     views = [SimpleNamespace(block_table=t, page_size=page) for t in tables]
+    # --chunk C: queries see the keys of their own chunk of C positions; --bias: a slope per head on the
+    # distance (2^(-8 (h + 1) / H)) and a sink per head
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device="cuda") if a.bias else None
+    sinks = torch.randn(H, device="cuda") if a.bias else None
     fn = lambda i: ops.paged_attention(q, kc, vc, views[i], ctx, D ** -0.5, 0, num_splits=a.splits or None,
-                                     backend=a.backend or None)
+                                     backend=a.backend or None, chunk=a.chunk, slopes=slopes, sinks=sinks)
     us = _time(fn, copies, a.iters, a.graph)
-    kv_bytes = B * kv_len * 2 * Hkv * D * 2
-    flops = 4.0 * B * H * D * (q_len * kv_len - q_len * (q_len - 1) / 2)
+    pos = torch.arange(kv_len - q_len, kv_len)
+    seen = float((pos % a.chunk + 1).sum()) if a.chunk else float((pos + 1).sum())     # visible (query, key) pairs of a request
+    kv_bytes = B * (min(kv_len, (kv_len - 1) % a.chunk + 1) if a.chunk and q_len == 1 else kv_len) * 2 * Hkv * D * 2
+    flops = 4.0 * B * H * D * seen
     return {"kernel": "attention_decode" if q_len == 1 else "attention_prefill", "batch": B, "q_len": q_len,
             "kv_len": kv_len, "heads": H, "kv_heads": Hkv, "head_dim": D, "us": round(us, 2),
             "gbs": round(kv_bytes / us / 1e3, 1), "tflops": round(flops / us / 1e6, 2)}
@@ -153,6 +159,8 @@ def main(argv=None):
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--backend", choices=["tcgen05", "mma", "simt"], default="",
                     help="attention: a slower kernel than the one the head size selects")
+    ap.add_argument("--chunk", type=int, default=0, help="attention: positions per chunk (0: plain causal)")
+    ap.add_argument("--bias", action="store_true", help="attention: a distance slope and a sink per head")
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)

@@ -821,7 +821,8 @@ def decode_splits(num_requests, max_kv_len, num_heads, num_kv_heads):
     return max(1, min(2 * num_sms() // blocks, max_kv_len // 128, 32))
 
 
-def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first=0, sinks=None):
+def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first=0, sinks=None, chunk=0,
+                   slopes=None):
     """The one-token requests of a mixed batch, by the tensor-core decode kernel."""
     T, H, D = q.shape
     Hkv = k_cache.shape[1]
@@ -839,7 +840,7 @@ def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, kee
         c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale), c_int(window),
         c_int(num_splits), _ptr(part_o), _ptr(part_ml), c_int(2 if cluster else 1), _ptr(work.dec_req),
         _ptr(work.dec_tok), c_int(n), c_int(0), c_int(_tma_pages(k_cache, v_cache)), c_int(keep_first), _ptr(sinks),
-        _stream()),
+        c_int(chunk), _ptr(slopes), _stream()),
         2 if num_splits > 1 and not cluster else 1)
 
 
@@ -867,15 +868,11 @@ def prefill_tile_queries(dtype, num_heads, num_kv_heads, head_dim, page_size=16)
     return 0
 
 
-#: the chunk mask and the distance bias live in the 32-bit attention kernel; the tensor-core kernels do not
-#: take them, so a mixer with either asks for no work lists
-BIASED_ATTENTION_ON_TENSOR_CORES = False
-
-
 def biased_attention_backends(dtype, head_dim, page_size) -> list:
-    """The attention kernels that take a chunk mask and a distance bias at this head size, the one
-    the engine picks first."""
-    return ["simt"]
+    """The attention kernels that take a chunk mask and a distance bias at this element type and head
+    size (all that take the plain case do), the one the engine picks first."""
+    first = attention_backend(dtype, head_dim, page_size)
+    return [first] + [b for b in ("mma", "simt") if b != first and (first != "simt")]
 
 
 def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None, backend=None, keep_first=0,
@@ -903,8 +900,6 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         raise ValueError("paged_attention: a chunk is positive and comes without a window")
     if slopes is not None and (slopes.dtype != torch.float32 or slopes.shape != (H,) or not slopes.is_cuda):
         raise TypeError("paged_attention: slopes are float32 [heads] on the device")
-    if (chunk or slopes is not None) and backend is None:
-        chosen = "simt"         # the chunk mask and the distance bias live in the 32-bit kernel
     if backend is not None and backend != chosen:
         if q.dtype != torch.bfloat16 or (backend == "tcgen05") or (backend == "mma" and chosen == "simt"):
             raise ValueError(f"attention backend {backend!r} does not take {q.dtype}, head size {D}, pages of {page}")
@@ -919,14 +914,14 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         tile_queries = prefill_tile_queries(q.dtype, H, Hkv, D, page)
         work = attention_work(ctx, tile_queries, q.device)
         if work.num_decode:
-            _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first, sinks)
+            _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first, sinks, chunk, slopes)
         if work.num_tiles:
             _check(lib, lib.ts_paged_attention_tcgen05(
                 _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
                 _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H), c_int(Hkv),
                 c_int(k_cache.shape[0]), c_int(page), c_int(view.block_table.stride(0)), c_float(scale),
                 c_int(window), _ptr(work.tile_req), _ptr(work.tile_q0), c_int(work.num_tiles),
-                c_int(tile_queries), c_int(keep_first), _ptr(sinks), _stream()))
+                c_int(tile_queries), c_int(keep_first), _ptr(sinks), c_int(chunk), _ptr(slopes), _stream()))
         return out
     if num_splits is None:
         if decode:
@@ -954,7 +949,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             tile_queries = rows // group if group < rows else 1
             work = attention_work(ctx, tile_queries, q.device)
             if work.num_decode:
-                _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first, sinks)
+                _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first, sinks, chunk, slopes)
             if not work.num_tiles:
                 return out
             tile_req, tile_q0, num_tiles = work.tile_req, work.tile_q0, work.num_tiles
@@ -964,7 +959,8 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale),
             c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml),
             c_int((2 if cluster else 1) if decode else 0), _ptr(tile_req), _ptr(tile_q0), c_int(num_tiles), c_int(tile_queries),
-            c_int(_tma_pages(k_cache, v_cache)), c_int(keep_first), _ptr(sinks), _stream()), launches)
+            c_int(_tma_pages(k_cache, v_cache)), c_int(keep_first), _ptr(sinks), c_int(chunk), _ptr(slopes), _stream()),
+            launches)
         return out
     lib = _attention(D)
     _check(lib, lib.ts_paged_attention_biased(

@@ -146,8 +146,6 @@ class Attention(Mixer):
     accepts_scaled_rows = True
 
     def work_tile_queries(self, dtype, page_size):
-        if self._biased() and not ops.BIASED_ATTENTION_ON_TENSOR_CORES:
-            return 0
         return ops.prefill_tile_queries(dtype, self.num_heads, self.num_kv_heads, self.stored_dim, page_size)
 
     def _forward_general(self, h, ctx, call):
