@@ -421,6 +421,23 @@ def _time_us(fn, iters=20):
     return start.elapsed_time(end) * 1e3 / iters
 
 
+def _time_graph_us(fn, iters=20):
+    """Device time of ``fn`` per call, its launches replayed from a CUDA graph as the engine replays a decode
+    step: the host's time between launches is not in it."""
+    import torch
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(iters):
+                fn()
+    torch.cuda.current_stream().wait_stream(side)
+    return _time_us(graph.replay, iters=5) / iters
+
+
 def kernel_table(width, peaks):
     """The design's own kernels beside the like kernels of Qwen3 at this width, one launch each
     (operands larger than L2 where the size allows: 2,048 tokens of prefill; at decode the state
@@ -621,8 +638,9 @@ def tarivik_kernel_table(width, peaks):
     def frac(key, us, roof):
         out[key] = {"us": round(us, 1), "roofline_us": round(roof, 2), "frac": round(roof / us, 3)}
 
-    for name, lengths, starts in (("prefill_2048", [2048], [0]), ("decode_b8", [1] * 8, [2048] * 8)):
+    for name, lengths, starts in (("prefill_2048", [2048], [0]), ("decode_b8", [1] * 8, [2047] * 8)):
         T, B = sum(lengths), len(lengths)
+        timer = _time_us if T > B else _time_graph_us          # a decode step's launches are replayed from a graph
         kv_len, page = starts[0] + lengths[0], 64
         pages_per = -(-kv_len // page)
         cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=dev)
@@ -638,7 +656,7 @@ def tarivik_kernel_table(width, peaks):
             sc.num_tokens, sc.num_requests, sc.max_q_len, sc.max_kv_len = T, B, max(lengths), kv_len
             sc.cu_q, sc.kv_lens = cu, torch.full((B,), kv_len, dtype=torch.int32, device=dev)
             sc.host = {"cu_q": cu.tolist(), "kv_lens": [kv_len] * B}
-            us = _time_us(lambda: ops.paged_attention(q, kc, vc, view, sc, D ** -0.5, **kw))
+            us = timer(lambda: ops.paged_attention(q, kc, vc, view, sc, D ** -0.5, **kw))
             roof = (4.0 * H * D * seen / (peaks["bf16_tflops"] * 1e6) if T > B
                     else B * seen * 2 * G * D * 2 / (peaks["hbm_gbs"] * 1e3))
             return us, roof
@@ -665,7 +683,7 @@ def tarivik_kernel_table(width, peaks):
         proj = torch.randn(T, Hh * n + Hh * nv, device=dev).to(bf)
         z, low = torch.randn(T, Hh * n, device=dev) + 3, torch.rand(Hh * n, device=dev)
         state, wv = torch.zeros(B, Hh, n, nv, device=dev), torch.ones(nv, device=dev, dtype=bf)
-        frac(f"hgrn2_scan_{name}", _time_us(lambda: ops.linear_attention(
+        frac(f"hgrn2_scan_{name}", timer(lambda: ops.linear_attention(
             proj[:, :Hh * n], None, proj[:, Hh * n:], None, state, ctx, Hh, n, nv, bf, decay_logits=z, lower=low, tied_key=True,
             input_activation="q", norm_weight=wv, eps=1e-6)), scan_roof(Hh, n, nv, (Hh * n + 2 * Hh * nv) * 2 + Hh * n * 4))
         Hm, n, nv = ml["heads"], ml["dim"], ml["vdim"]
@@ -680,7 +698,7 @@ def tarivik_kernel_table(width, peaks):
                                      state, ctx, Hm, n, cols, bf, token_keep=keep_, token_write=write, q_scale=n ** -0.5,
                                      value_width=nv, raw=True)
             return ops.mlstm_finish(o, floor, wn, proj[:, 2 * Hm * n + Hm * nv:], 1e-6, Hm, nv, bf)
-        frac(f"mlstm_gates_scan_finish_{name}", _time_us(mlstm), scan_roof(Hm, n, nv, (2 * Hm * n + 3 * Hm * nv) * 2))
+        frac(f"mlstm_gates_scan_finish_{name}", timer(mlstm), scan_roof(Hm, n, nv, (2 * Hm * n + 3 * Hm * nv) * 2))
         Hs, nv, n, taps = right["heads"], right["vdim"], right["state"], right["conv"]
         inner, C = Hs * nv, Hs * nv + 2 * right["groups"] * n
         proj = torch.randn(T, inner + C, device=dev).to(bf)
@@ -691,17 +709,16 @@ def tarivik_kernel_table(width, peaks):
 
         def ssm():
             xbc = ops.causal_conv(proj[:, inner:], cw, conv_state, ctx, bf, bias=cb, activation="silu")
-            keep_, write = ops.ssm_gates(dt_raw, dtb, alog, Hs)
             o = ops.linear_attention(xbc[:, inner + n * right["groups"]:], xbc[:, inner:inner + n * right["groups"]], xbc[:, :inner],
-                                     None, state, ctx, Hs, n, nv, bf, token_keep=keep_, token_write=write,
+                                     None, state, ctx, Hs, n, nv, bf, step_sizes=(dt_raw, dtb, alog),
                                      qk_group=Hs // right["groups"], raw=True)
             return ops.ssm_finish(o, xbc[:, :inner], skip, proj[:, :inner], wn, right["norm_groups"], 1e-6, Hs, nv, bf)
-        frac(f"state_space_conv_scan_finish_{name}", _time_us(ssm), scan_roof(Hs, n, nv, (2 * inner + C) * 2))
+        frac(f"state_space_conv_scan_finish_{name}", timer(ssm), scan_roof(Hs, n, nv, (2 * inner + C) * 2))
         Hl, n, nv = lig["heads"], lig["dim"], lig["vdim"]
         proj = torch.randn(T, 2 * Hl * n + 2 * Hl * nv, device=dev).to(bf)
         state, wj = torch.zeros(B, Hl, n, nv, device=dev), torch.ones(Hl * nv, device=dev)
         decay = torch.full((Hl,), 0.99, device=dev)
-        frac(f"delilorn_lightning_scan_{name}", _time_us(lambda: ops.linear_attention(
+        frac(f"delilorn_lightning_scan_{name}", timer(lambda: ops.linear_attention(
             proj[:, :Hl * n], proj[:, Hl * n:2 * Hl * n], proj[:, 2 * Hl * n:2 * Hl * n + Hl * nv], proj[:, 2 * Hl * n + Hl * nv:],
             state, ctx, Hl, n, nv, bf, decay=decay, norm_weight=wj, eps=1e-6, input_activation="silu", gate_activation="sigmoid",
             joint_norm=True)), scan_roof(Hl, n, nv, (2 * Hl * n + 3 * Hl * nv) * 2))
@@ -719,7 +736,7 @@ def tarivik_kernel_table(width, peaks):
             if kw:
                 tensors["correction"] = torch.zeros(E, device=dev)
             part.bind(tensors)
-            us = _time_us(lambda: ops.materialize(part.forward(h, None)))
+            us = timer(lambda: ops.materialize(part.forward(h, None)))
             frac(f"{key}_{name}", us, 2.0 * mats * T * top * width * ffe / (peaks["bf16_tflops"] * 1e6) if T > B
                  else mats * E * width * ffe * 2 / (peaks["hbm_gbs"] * 1e3))
         # what stands between two sub-layers
@@ -731,8 +748,8 @@ def tarivik_kernel_table(width, peaks):
         def between():
             ops.group_norm_add_(y, wn, 2, 1e-6, res)
             return ops.causal_conv(res, cw, cstate, ctx, bf, add_input=True)
-        frac(f"group_norm_add_and_input_conv_{name}", _time_us(between), T * width * (8 + 2 + 4 + 2) / (peaks["hbm_gbs"] * 1e3))
-        frac(f"delilorn_normed_add_rmsnorm_{name}", _time_us(lambda: ops.normed_add_rmsnorm(ops.NormedAddend(y, wf, 1e-6), res, wf, 1e-6, bf)),
+        frac(f"group_norm_add_and_input_conv_{name}", timer(between), T * width * (8 + 2 + 4 + 2) / (peaks["hbm_gbs"] * 1e3))
+        frac(f"delilorn_normed_add_rmsnorm_{name}", timer(lambda: ops.normed_add_rmsnorm(ops.NormedAddend(y, wf, 1e-6), res, wf, 1e-6, bf)),
              T * width * (8 + 2 + 2) / (peaks["hbm_gbs"] * 1e3))
     return out
 

@@ -272,7 +272,7 @@ __global__ void moe_gated_activate_kernel(const T* __restrict__ a, const float* 
   const size_t r = blockIdx.x;
   const T* row = a + r * (size_t)E * 2 * ff;
   T* dst = out + r * (size_t)E * ff;
-  for (int i = threadIdx.x; i < E * ff; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < E * ff; i += gridDim.y * blockDim.x) {
     const int e = i / ff, j = i % ff;
     const float g = gates ? gates[r * E + e] : 1.f;
     float y = 0.f;
@@ -593,10 +593,13 @@ TS_EXPORT int ts_moe_route_scored(const float* logits, const float* correction, 
 TS_EXPORT int ts_moe_gated_activate(int dtype, const void* a, const float* gates, int rows, int E, int ff, void* out,
                                     cudaStream_t stream) {
   TS_REQUIRE(rows > 0 && E > 0 && ff > 0 && a && out, "moe_gated_activate: empty input");
+  // a row's columns over several blocks (four elements a thread), so that a step of few rows still fills the SMs
+  const long long tiles = ((long long)E * ff + 1023) / 1024;
+  const dim3 grid(rows, (unsigned)(tiles < 64 ? tiles : 64));
   if (dtype == TS_F32)
-    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<float>, rows, 256, 0, stream, (const float*)a, gates, E, ff, (float*)out);
+    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<float>, grid, 256, 0, stream, (const float*)a, gates, E, ff, (float*)out);
   else if (dtype == TS_BF16)
-    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<__nv_bfloat16>, rows, 256, 0, stream, (const __nv_bfloat16*)a, gates, E, ff,
+    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)a, gates, E, ff,
               (__nv_bfloat16*)out);
   else return ts_fail("moe_gated_activate: unknown dtype %d", dtype);
   return 0;

@@ -8,7 +8,8 @@
 // channel a_t = l + (1 - l) sigmoid(z_t), and then k_t may be tied to it, k_t = 1 - a_t), or one
 // number per head and token that the caller made (`tok_keep`, with a factor `tok_write` on k_t:
 // S_t = keep_t S_(t-1) + write_t k_t v_t^T, the form of selective state spaces and of matrix
-// memories with an exponential input gate).  Several heads may share one q and k (`qk_group`).
+// memories with an exponential input gate; for a selective state space the kernel may make both itself
+// from the 32-bit step-size logits: dt = softplus(raw + bias_h), keep = exp(-exp(rate_h) dt), write = dt).  Several heads may share one q and k (`qk_group`).
 // The values may get constant columns behind the ones the caller brings (`v_width` < value size: a
 // column of ones, then zeros), so that S^T q also holds sum_t (...) k_t . q, a normaliser.
 // q and k may get rotary positions on their first rotary_dim elements and a constant factor
@@ -100,6 +101,8 @@ struct ScanParams {
   int qk_group;                           // heads that share one q and one k (1: every head its own)
   int v_width;                            // value columns the caller brings per head; behind them a column of ones, then zeros
   int finish;                             // 0: the 32-bit outputs in raw_out are all the caller wants
+  const float* step_raw; long long ld_step;   // [T, H] or null: step-size logits, in place of tok_keep / tok_write
+  VecParam step_bias, step_rate;              // [H] each: dt = softplus(raw + bias), keep = exp(-exp(rate) dt), write = dt
 };
 
 enum { DECAY_HEAD = 0, DECAY_CHANNEL = 1, DECAY_TOKEN = 2 };
@@ -114,6 +117,7 @@ __device__ __forceinline__ float gate_factor(float g, int gate_act) {
 enum { SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_FROM_SEGMENT = 2 };
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
 // Ask for the 128-byte lines of `rows` runs of `bytes` bytes, `stride` bytes apart, to be brought
 // into L1: the staging of the next chunk then finds its operands there instead of waiting for L2
@@ -214,8 +218,14 @@ __global__ void __launch_bounds__(MAX_THREADS, TS_SCAN_BLOCKS) linear_attention_
       const T* qt = q + t * p.ldq;
       float k_factor = p.k_scale;
       if (DECAY == DECAY_TOKEN) {
-        k_factor *= __ldg(p.tok_write + t * p.H + h);
-        if (lane == 0) s_keep[tok] = __ldg(p.tok_keep + t * p.H + h);
+        if (p.step_raw) {
+          const float dt = softplus(__ldg(p.step_raw + t * p.ld_step + h) + p.step_bias[h]);
+          k_factor *= dt;
+          if (lane == 0) s_keep[tok] = expf(-expf(p.step_rate[h]) * dt);
+        } else {
+          k_factor *= __ldg(p.tok_write + t * p.H + h);
+          if (lane == 0) s_keep[tok] = __ldg(p.tok_keep + t * p.H + h);
+        }
       }
       if (half > 0) {
         const size_t at = (size_t)__ldg(p.positions + t) * half;
@@ -516,15 +526,17 @@ TS_EXPORT int ts_linear_attention(int dtype, const void* q, long long ldq, const
                                   int H, int vdim, int seg_len, float* seg_state, float* seg_decay, int max_segments,
                                   int num_tokens, float* raw_out, int in_act, int gate_act, int joint_norm,
                                   const float* lower, int tied_key, const float* tok_keep, const float* tok_write,
-                                  int qk_group, int v_width, int finish, cudaStream_t stream) {
+                                  int qk_group, int v_width, int finish, const float* step_raw, long long ld_step,
+                                  const void* step_bias, const void* step_rate, int step_vec_is_f32, cudaStream_t stream) {
   TS_REQUIRE(num_requests > 0 && H > 0 && vdim > 0, "linear_attention: empty input");
+  TS_REQUIRE(step_raw == nullptr || (step_bias && step_rate && ld_step >= H), "linear_attention: step-size logits come with a bias and a rate per head");
   const int cols = block_columns(vdim);
   const int col_tiles = (vdim + cols - 1) / cols;
   TS_REQUIRE((col_tiles > 1 || joint_norm || !finish) == (raw_out != nullptr) && num_tokens > 0,
              "linear_attention: heads of more than %d value columns, a norm over all heads, and outputs that the caller "
              "finishes, come with a 32-bit scratch for their outputs, others without", cols);
-  TS_REQUIRE((z != nullptr) + (decay != nullptr) + (tok_keep != nullptr) == 1,
-             "linear_attention: per-channel logits, per-head decays or per-token decays");
+  TS_REQUIRE((z != nullptr) + (decay != nullptr) + (tok_keep != nullptr) + (step_raw != nullptr) == 1,
+             "linear_attention: per-channel logits, per-head decays, per-token decays or step-size logits");
   TS_REQUIRE(tok_keep == nullptr || tok_write != nullptr, "linear_attention: per-token decays come with per-token factors on k");
   TS_REQUIRE(z == nullptr || lower != nullptr || tau > 0.f, "linear_attention: tau must be positive");
   TS_REQUIRE(lower == nullptr || z != nullptr, "linear_attention: a lower bound belongs to per-channel logits");
@@ -541,8 +553,9 @@ TS_EXPORT int ts_linear_attention(int dtype, const void* q, long long ldq, const
   ScanParams p{q, k, v, gate, ldq, ldk, ldv, ldg, z, ldz, decay, z && !lower ? 1.f / tau : 0.f, positions, cos, sin, rotary_dim,
                q_scale, k_scale, state, state_slots, fresh, cu_q, norm_weight, norm_weight_is_f32, eps, out, ldo, H, vdim,
                seg_len, seg_state, seg_decay, max_segments, cols, col_tiles, raw_out, in_act, gate_act, joint_norm,
-               lower, tied_key, tok_keep, tok_write, qk_group, v_width, finish};
-  const int mode = z ? DECAY_CHANNEL : (tok_keep ? DECAY_TOKEN : DECAY_HEAD);
+               lower, tied_key, tok_keep, tok_write, qk_group, v_width, finish, step_raw, ld_step,
+               VecParam{step_bias, step_vec_is_f32}, VecParam{step_rate, step_vec_is_f32}};
+  const int mode = z ? DECAY_CHANNEL : (tok_keep || step_raw ? DECAY_TOKEN : DECAY_HEAD);
   if (dtype == TS_F32) {
     if (mode == DECAY_CHANNEL) return launch_scan<float, DECAY_CHANNEL>(p, num_requests, num_tokens, stream);
     if (mode == DECAY_TOKEN) return launch_scan<float, DECAY_TOKEN>(p, num_requests, num_tokens, stream);

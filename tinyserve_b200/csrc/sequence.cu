@@ -18,7 +18,6 @@
 //  * ts_mlstm_gates: the stabilised gates of a matrix memory with exponential input gate:
 //    m_t = max(f_t + m_(t-1), i_t), keep_t = exp(f_t + m_(t-1) - m_t), write_t = exp(i_t - m_t),
 //    floor_t = exp(-m_t); i and f capped by cap tanh(. / cap), f through log-sigmoid; m is state.
-//  * ts_ssm_gates: dt = softplus(raw + bias), keep = exp(-exp(A_log) dt), write = dt.
 //  * ts_mlstm_finish: o / (max(|n . q|, floor) + 1e-6), RMS per head, weight, sigmoid gate.
 //  * ts_ssm_finish: (y + D x) silu(z), RMS in groups over all heads, weight.
 #include "common.cuh"
@@ -50,7 +49,6 @@ struct RowsOut {
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
-__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
 // ------------------------------------------------------------------ learned positions
 __global__ void add_position_rows_kernel(float* __restrict__ residual, VecParam table, const int* __restrict__ positions,
@@ -143,30 +141,46 @@ __global__ void __launch_bounds__(CONV_THREADS) causal_conv_kernel(ConvParams p)
 }
 
 // ------------------------------------------------------------------ RMS norm in groups
-// a warp per group, round robin; y = x / sqrt(mean(x^2) + eps) * w over each group of n / groups
+// a block per (row, group); y = x / sqrt(mean(x^2) + eps) * w over each group of n / groups.  A thread keeps
+// its first ROW_HOLD elements in registers between the sum and the scaling, and reads any further ones twice.
+constexpr int ROW_HOLD = 8;
+
+// threads of a block that walks `per` elements of a row: four elements a thread, 32 to 256 threads
+inline int row_threads(int per) { return per >= 1024 ? 256 : (per >= 512 ? 128 : (per >= 256 ? 64 : 32)); }
+
 template <bool ADD>
 __global__ void group_norm_kernel(Rows x, VecParam w, const int* __restrict__ rows, int groups, int n, float eps,
                                   RowsOut out, float* __restrict__ residual) {
+  __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const size_t o = blockIdx.x;
   const size_t t = rows ? (size_t)rows[o] : o;
-  const int per = n / groups;
-  for (int g = warp; g < groups; g += warps) {
-    float acc = 0.f;
-    for (int i = lane; i < per; i += 32) {
-      const float v = x.at(t, g * per + i);
-      acc = fmaf(v, v, acc);
-    }
-    const float rstd = rsqrtf(warp_sum(acc) / (float)per + eps);
-    for (int i = lane; i < per; i += 32) {
-      const int col = g * per + i;
-      const float y = x.at(t, col) * rstd * w[col];
-      if (ADD) residual[t * n + col] += y;
-      else out.put(o, col, y);
-    }
+  const int per = n / groups, base = blockIdx.y * per;
+  float held[ROW_HOLD], acc = 0.f;
+#pragma unroll
+  for (int j = 0; j < ROW_HOLD; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    held[j] = i < per ? x.at(t, base + i) : 0.f;
+    acc = fmaf(held[j], held[j], acc);
   }
+  for (int i = threadIdx.x + ROW_HOLD * blockDim.x; i < per; i += blockDim.x) {
+    const float v = x.at(t, base + i);
+    acc = fmaf(v, v, acc);
+  }
+  const float rstd = rsqrtf(block_sum(acc, scratch) / (float)per + eps);
+  auto put = [&](int i, float v) {
+    const int col = base + i;
+    const float y = v * rstd * w[col];
+    if (ADD) residual[t * n + col] += y;
+    else out.put(o, col, y);
+  };
+#pragma unroll
+  for (int j = 0; j < ROW_HOLD; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < per) put(i, held[j]);
+  }
+  for (int i = threadIdx.x + ROW_HOLD * blockDim.x; i < per; i += blockDim.x) put(i, x.at(t, base + i));
 }
 
 // ------------------------------------------------------------------ a x + b y
@@ -296,19 +310,6 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ raw, long long ld, 
   if (lane == 0) *ms = m;
 }
 
-// ------------------------------------------------------------------ step sizes of a selective state space
-__global__ void ssm_gates_kernel(Rows dt_raw, VecParam dt_bias, VecParam a_log, int H, long long count,
-                                 float* __restrict__ keep, float* __restrict__ write) {
-  pdl_trigger();
-  pdl_wait();
-  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  if (i >= count) return;
-  const int h = (int)(i % H);
-  const float dt = softplus_f(dt_raw.at((size_t)(i / H), h) + dt_bias[h]);
-  keep[i] = expf(-expf(a_log[h]) * dt);
-  write[i] = dt;
-}
-
 // ------------------------------------------------------------------ what follows the scan of a matrix memory
 // raw [T, H, wide] 32-bit: columns [0, vdim) the numerator S^T q, column vdim the product n . q
 __global__ void mlstm_finish_kernel(const float* __restrict__ raw, int wide, const float* __restrict__ floor_,
@@ -337,28 +338,37 @@ __global__ void mlstm_finish_kernel(const float* __restrict__ raw, int wide, con
   }
 }
 
-// raw [T, H vdim] 32-bit y of the scan; x the scan's values; z the gate
+// raw [T, H vdim] 32-bit y of the scan; x the scan's values; z the gate; a block per (token, norm group)
 __global__ void ssm_finish_kernel(const float* __restrict__ raw, Rows x, VecParam skip, Rows z, VecParam weight, int groups,
                                   float eps, RowsOut out, int H, int vdim) {
+  __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const size_t t = blockIdx.x;
-  const int n = H * vdim, per = n / groups;
-  for (int g = warp; g < groups; g += warps) {
-    float acc = 0.f;
-    for (int i = lane; i < per; i += 32) {
-      const int col = g * per + i;
-      const float y = (raw[t * n + col] + skip[col / vdim] * x.at(t, col)) * silu_f(z.at(t, col));
-      acc = fmaf(y, y, acc);
-    }
-    const float rstd = rsqrtf(warp_sum(acc) / (float)per + eps);
-    for (int i = lane; i < per; i += 32) {
-      const int col = g * per + i;
-      const float y = (raw[t * n + col] + skip[col / vdim] * x.at(t, col)) * silu_f(z.at(t, col));
-      out.put(t, col, y * rstd * weight[col]);
-    }
+  const int n = H * vdim, per = n / groups, base = blockIdx.y * per;
+  auto gated = [&](int i) {
+    const int col = base + i;
+    return (raw[t * n + col] + skip[col / vdim] * x.at(t, col)) * silu_f(z.at(t, col));
+  };
+  float held[ROW_HOLD], acc = 0.f;
+#pragma unroll
+  for (int j = 0; j < ROW_HOLD; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    held[j] = i < per ? gated(i) : 0.f;
+    acc = fmaf(held[j], held[j], acc);
   }
+  for (int i = threadIdx.x + ROW_HOLD * blockDim.x; i < per; i += blockDim.x) {
+    const float y = gated(i);
+    acc = fmaf(y, y, acc);
+  }
+  const float rstd = rsqrtf(block_sum(acc, scratch) / (float)per + eps);
+#pragma unroll
+  for (int j = 0; j < ROW_HOLD; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < per) out.put(t, base + i, held[j] * rstd * weight[base + i]);
+  }
+  for (int i = threadIdx.x + ROW_HOLD * blockDim.x; i < per; i += blockDim.x)
+    out.put(t, base + i, gated(i) * rstd * weight[base + i]);
 }
 
 }  // namespace
@@ -397,9 +407,8 @@ TS_EXPORT int ts_causal_conv(const void* x, long long ldx, int x_is_f32, void* y
 // rows null: every row of x [num_out, n]; else out[o] = norm(x[rows[o]])
 TS_EXPORT int ts_group_norm(const void* x, long long ldx, int x_is_f32, const void* w, int w_is_f32, const int* rows,
                             int groups, int n, float eps, void* out, int out_is_f32, int num_out, cudaStream_t stream) {
-  TS_REQUIRE(num_out > 0 && n > 0 && groups > 0 && n % groups == 0, "group_norm: %d columns in %d groups", n, groups);
-  const int threads = 32 * (groups >= 8 ? 8 : groups);
-  TS_LAUNCH("group_norm", group_norm_kernel<false>, num_out, threads, 0, stream, Rows{x, ldx, x_is_f32},
+  TS_REQUIRE(num_out > 0 && n > 0 && groups > 0 && groups <= 65535 && n % groups == 0, "group_norm: %d columns in %d groups", n, groups);
+  TS_LAUNCH("group_norm", group_norm_kernel<false>, dim3(num_out, groups), row_threads(n / groups), 0, stream, Rows{x, ldx, x_is_f32},
             VecParam{w, w_is_f32}, rows, groups, n, eps, RowsOut{out, (long long)n, out_is_f32}, (float*)nullptr);
   return 0;
 }
@@ -407,9 +416,8 @@ TS_EXPORT int ts_group_norm(const void* x, long long ldx, int x_is_f32, const vo
 // residual [T, n] (float, in place) += norm(y)
 TS_EXPORT int ts_group_norm_add(const void* y, long long ldy, int y_is_f32, const void* w, int w_is_f32, int groups, int n,
                                 float eps, float* residual, int num_tokens, cudaStream_t stream) {
-  TS_REQUIRE(num_tokens > 0 && n > 0 && groups > 0 && n % groups == 0, "group_norm_add: %d columns in %d groups", n, groups);
-  const int threads = 32 * (groups >= 8 ? 8 : groups);
-  TS_LAUNCH("group_norm_add", group_norm_kernel<true>, num_tokens, threads, 0, stream, Rows{y, ldy, y_is_f32},
+  TS_REQUIRE(num_tokens > 0 && n > 0 && groups > 0 && groups <= 65535 && n % groups == 0, "group_norm_add: %d columns in %d groups", n, groups);
+  TS_LAUNCH("group_norm_add", group_norm_kernel<true>, dim3(num_tokens, groups), row_threads(n / groups), 0, stream, Rows{y, ldy, y_is_f32},
             VecParam{w, w_is_f32}, (const int*)nullptr, groups, n, eps, RowsOut{nullptr, 0, 0}, residual);
   return 0;
 }
@@ -426,7 +434,7 @@ TS_EXPORT int ts_axpby(const void* x, const void* y, int in_is_f32, float a, flo
 TS_EXPORT int ts_gate_columns(const void* x, const void* gate, long long ldg, int is_f32, void* out, int H, int stored,
                               int vdim, int num_tokens, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && H > 0 && vdim > 0 && stored >= vdim && x && gate && out, "gate_columns: operands do not fit");
-  TS_LAUNCH("gate_columns", gate_columns_kernel, num_tokens, H * vdim >= 1024 ? 256 : 128, 0, stream,
+  TS_LAUNCH("gate_columns", gate_columns_kernel, num_tokens, H * vdim >= 2048 ? 512 : (H * vdim >= 1024 ? 256 : 128), 0, stream,
             Rows{x, (long long)H * stored, is_f32}, Rows{gate, ldg, is_f32}, RowsOut{out, (long long)H * vdim, is_f32}, H, stored,
             vdim);
   return 0;
@@ -442,7 +450,7 @@ TS_EXPORT int ts_joint_norm_kvwrite(int is_f32, const void* q, long long ldq, co
   TS_REQUIRE(slot_mapping == nullptr || (k_cache && v_cache && page_size > 0), "joint_norm_kvwrite: no cache to write");
   JointNorm p{Rows{q, ldq, is_f32}, Rows{k, ldk, is_f32}, Rows{v, ldv, is_f32}, VecParam{qw, w_is_f32},
               VecParam{kw, w_is_f32}, eps, H, G, dim, vdim, stored, page_size, q_out, k_cache, v_cache, slot_mapping, is_f32};
-  TS_LAUNCH("joint_norm_kvwrite", joint_norm_kvwrite_kernel, num_tokens, 128, 0, stream, p);
+  TS_LAUNCH("joint_norm_kvwrite", joint_norm_kvwrite_kernel, num_tokens, H * dim >= 2048 ? 512 : (H * dim >= 512 ? 256 : 128), 0, stream, p);
   return 0;
 }
 
@@ -454,15 +462,6 @@ TS_EXPORT int ts_mlstm_gates(const float* raw, long long ld, float cap, float* m
   const int warps = 4;
   TS_LAUNCH("mlstm_gates", mlstm_gates_kernel, (num_requests * H + warps - 1) / warps, warps * 32, 0, stream, raw, ld, cap,
             m_state, state_slots, fresh, cu_q, num_requests, H, keep, write, floor_);
-  return 0;
-}
-
-TS_EXPORT int ts_ssm_gates(const void* dt_raw, long long ld, int is_f32, const void* dt_bias, const void* a_log,
-                           int w_is_f32, int H, int num_tokens, float* keep, float* write, cudaStream_t stream) {
-  TS_REQUIRE(num_tokens > 0 && H > 0 && dt_raw && dt_bias && a_log && keep && write, "ssm_gates: empty input");
-  const long long count = (long long)num_tokens * H;
-  TS_LAUNCH("ssm_gates", ssm_gates_kernel, (int)((count + 255) / 256), 256, 0, stream, Rows{dt_raw, ld, is_f32},
-            VecParam{dt_bias, w_is_f32}, VecParam{a_log, w_is_f32}, H, count, keep, write);
   return 0;
 }
 
@@ -482,11 +481,10 @@ TS_EXPORT int ts_mlstm_finish(const float* raw, int wide, const float* floor_, c
 TS_EXPORT int ts_ssm_finish(const float* raw, const void* x, long long ldx, const void* skip, const void* z, long long ldz,
                             const void* weight, int w_is_f32, int io_is_f32, int groups, float eps, void* out, int H,
                             int vdim, int num_tokens, cudaStream_t stream) {
-  TS_REQUIRE(num_tokens > 0 && H > 0 && vdim > 0 && groups > 0 && (H * vdim) % groups == 0,
+  TS_REQUIRE(num_tokens > 0 && H > 0 && vdim > 0 && groups > 0 && groups <= 65535 && (H * vdim) % groups == 0,
              "ssm_finish: %d columns in %d groups", H * vdim, groups);
   TS_REQUIRE(raw && x && skip && z && weight && out, "ssm_finish: a null operand");
-  const int threads = 32 * (groups >= 8 ? 8 : groups);
-  TS_LAUNCH("ssm_finish", ssm_finish_kernel, num_tokens, threads, 0, stream, raw, Rows{x, ldx, io_is_f32},
+  TS_LAUNCH("ssm_finish", ssm_finish_kernel, dim3(num_tokens, groups), row_threads(H * vdim / groups), 0, stream, raw, Rows{x, ldx, io_is_f32},
             VecParam{skip, w_is_f32}, Rows{z, ldz, io_is_f32}, VecParam{weight, w_is_f32}, groups, eps,
             RowsOut{out, (long long)H * vdim, io_is_f32}, H, vdim);
   return 0;

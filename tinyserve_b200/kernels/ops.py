@@ -1311,7 +1311,7 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
                      decay_logits=None, tau=1.0, rotary=None, q_scale=1.0, k_scale=1.0, norm_weight=None, eps=0.0,
                      segment=None, input_activation=None, gate_activation="silu", joint_norm=False,
                      lower=None, tied_key=False, token_keep=None, token_write=None, qk_group=1, value_width=None,
-                     raw=False):
+                     raw=False, step_sizes=None):
     """Per request and head S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over this step's
     tokens, from and to ``state`` [slots, H, key_dim, value_dim] (float32) at the requests' state
     slots (``ctx.state_slots``, ``ctx.fresh``, ``ctx.cu_q``); returns [T, H * value_dim] =
@@ -1326,7 +1326,9 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
     the operands that pass through silu, as a string of the letters q, k, v.
     ``lower`` float32 [H * key_dim] (with ``decay_logits``): a = lower + (1 - lower) sigmoid(z); with
     ``tied_key`` k = 1 - a and ``k`` is None.  ``token_keep`` / ``token_write`` float32 [T, H]: the decay of
-    (token, head) and a factor on its k, S_t = keep_t S_(t-1) + write_t k_t v_t^T.  ``qk_group``: heads
+    (token, head) and a factor on its k, S_t = keep_t S_(t-1) + write_t k_t v_t^T.  ``step_sizes`` (raw, bias,
+    rate), raw float32 [T, H] (a column range may be given), bias and rate [H]: the kernel makes both itself,
+    dt = softplus(raw + bias), keep = exp(-exp(rate) dt), write = dt.  ``qk_group``: heads
     that share one q and one k (q, k [T, H / qk_group * key_dim]).  ``value_width`` < value_dim: v holds
     that many columns per head, the state's next column is fed ones (so that column of S^T q is
     sum of the k . q terms) and the rest zeros.  ``raw``: returns the 32-bit S^T q [T, H * value_dim]
@@ -1345,8 +1347,16 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
         raise ValueError("linear_attention: q, k, v do not have heads x size columns")
     if state.dtype != torch.float32 or tuple(state.shape[1:]) != (H, key_dim, value_dim) or not state.is_contiguous():
         raise TypeError("linear_attention: the state is contiguous float32 [slots, H, key_dim, value_dim]")
-    if (decay is not None) + (decay_logits is not None) + (token_keep is not None) != 1:
-        raise ValueError("linear_attention: per-head decays, per-channel logits or per-token decays")
+    if (decay is not None) + (decay_logits is not None) + (token_keep is not None) + (step_sizes is not None) != 1:
+        raise ValueError("linear_attention: per-head decays, per-channel logits, per-token decays or step sizes")
+    step_raw = step_bias = step_rate = None
+    if step_sizes is not None:
+        step_raw, step_bias, step_rate = step_sizes
+        _cuda(step_raw, step_bias, step_rate)
+        if step_raw.dtype != torch.float32 or tuple(step_raw.shape) != (T, H) or step_raw.stride(1) != 1:
+            raise TypeError("linear_attention: step-size logits are float32 [T, H]")
+        if step_bias.dtype != step_rate.dtype or step_bias.numel() != H or step_rate.numel() != H:
+            raise TypeError("linear_attention: a step-size bias and a rate per head, of one type")
     if decay_logits is not None and (decay_logits.dtype != torch.float32 or decay_logits.shape[1] != H * key_dim):
         raise TypeError("linear_attention: decay logits are float32 [T, H * key_dim]")
     if lower is not None and (lower.dtype != torch.float32 or lower.numel() != H * key_dim or decay_logits is None):
@@ -1387,7 +1397,8 @@ def linear_attention(q, k, v, gate, state, ctx, num_heads, key_dim, value_dim, o
         _ptr(seg_decay), c_int(max_segments), c_int(T), _ptr(raw_out), c_int(acts[input_activation]),
         c_int(1 if gate_activation == "sigmoid" else 0), c_int(1 if joint_norm else 0), _ptr(lower),
         c_int(1 if tied_key else 0), _ptr(token_keep), _ptr(token_write), c_int(qk_group), c_int(vw),
-        c_int(0 if raw else 1), _stream()),
+        c_int(0 if raw else 1), _ptr(step_raw), c_longlong(step_raw.stride(0) if step_raw is not None else 0),
+        _ptr(step_bias), _ptr(step_rate), c_int(_f32(step_bias) if step_bias is not None else 0), _stream()),
         (3 if seg_len else 1) + int(wide and not raw))
     return raw_out if raw else out
 
@@ -1724,19 +1735,6 @@ def mlstm_gates(raw, cap, m_state, ctx, num_heads):
                                    _ptr(ctx.fresh), _ptr(ctx.cu_q), c_int(ctx.num_requests), c_int(H), _ptr(keep), _ptr(write),
                                    _ptr(floor), _stream()))
     return keep, write, floor
-
-
-def ssm_gates(dt_raw, dt_bias, a_log, num_heads):
-    """dt = softplus(dt_raw + dt_bias); returns float32 [T, H] keep = exp(-exp(a_log) dt) and write = dt."""
-    _cuda(dt_raw, dt_bias, a_log)
-    T, H = dt_raw.shape[0], num_heads
-    if dt_raw.shape[1] != H or dt_raw.stride(1) != 1 or dt_bias.shape != (H,) or a_log.shape != (H,) or dt_bias.dtype != a_log.dtype:
-        raise TypeError("ssm_gates: dt_raw [T, H], dt_bias and a_log [H] of one dtype")
-    keep, write = (torch.empty(T, H, dtype=torch.float32, device=dt_raw.device) for _ in range(2))
-    lib = _sequence()
-    _check(lib, lib.ts_ssm_gates(_ptr(dt_raw), c_longlong(dt_raw.stride(0)), c_int(_f32(dt_raw)), _ptr(dt_bias), _ptr(a_log),
-                                 c_int(_f32(a_log)), c_int(H), c_int(T), _ptr(keep), _ptr(write), _stream()))
-    return keep, write
 
 
 def mlstm_finish(raw, floor, weight, gate, eps, num_heads, value_dim, out_dtype):

@@ -308,11 +308,11 @@ class Mamba2(Mixer):
         conv_state = ctx.state(call.state_of("conv")) if self.taps > 1 else None
         xbc = ops.causal_conv(proj[:, inner:], self.w["conv.weight"], conv_state, ctx, ctx.dtype, bias=self.w["conv.bias"],
                               activation="silu")
-        keep, write = ops.ssm_gates(dt_raw, self.w["dt_bias"], self.w["a_log"], H)
         x = xbc[:, :inner]
+        # (the scan makes the step sizes, the decays and the factors on B from the logits while it stages a token)
         raw = ops.linear_attention(xbc[:, inner + GN:], xbc[:, inner:inner + GN], x, None, ctx.state(call.state), ctx, H,
-                                   self.state_dim, self.value_dim, ctx.dtype, token_keep=keep, token_write=write,
-                                   qk_group=H // self.groups, raw=True)
+                                   self.state_dim, self.value_dim, ctx.dtype,
+                                   step_sizes=(dt_raw, self.w["dt_bias"], self.w["a_log"]), qk_group=H // self.groups, raw=True)
         out = ops.ssm_finish(raw, x, self.w["skip"], proj[:, :inner], self.w["norm.weight"], self.norm_groups, self.eps, H,
                              self.value_dim, ctx.dtype)
         return ops.linear(out, self.w["o_proj.weight"], allow_pending=True)
