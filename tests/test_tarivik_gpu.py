@@ -109,6 +109,50 @@ def test_causal_convolution_in_portions_from_and_to_slots(dtype, tol, taps, form
         assert torch.equal(state[1].double().cpu(), x[T - taps + 1:].to(in_dtype).double())
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("H,groups,N,V", [(4, 1, 16, 24), (6, 2, 32, 8), (2, 2, 8, 64), (3, 3, 64, 40)])
+def test_scan_of_a_state_space_makes_its_step_sizes_itself(dtype, tol, H, groups, N, V):
+    """S_t = exp(-exp(rate_h) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t with dt_t = softplus(raw_t + bias_h),
+    heads of a group on one B and C: a sequence in one go against the same in portions through a state
+    slot that another request left full, beside a second request; rates and biases spread wide, so that
+    some heads forget within a token and others keep everything."""
+    from tinyserve_b200.kernels import ops
+    T = 150
+    x, B, C = draws(T, H * V, seed=1), draws(T, groups * N, seed=2), draws(T, groups * N, seed=3)
+    raw = (torch.randn(T, H, generator=torch.Generator().manual_seed(4)) * 2).float().double()
+    bias, rate = draws(H, seed=5, scale=2.0), draws(H, seed=6, scale=1.5)
+    dt = plain.softplus(raw + bias)
+    keep = torch.exp(-torch.exp(rate) * dt)
+    want = torch.zeros(T, H, V, dtype=torch.float64)
+    S = torch.zeros(H, N, V, dtype=torch.float64)
+    for t in range(T):
+        for h in range(H):
+            g = h // (H // groups)
+            S[h] = keep[t, h] * S[h] + dt[t, h] * torch.outer(B[t, g * N:(g + 1) * N], x[t, h * V:(h + 1) * V])
+            want[t, h] = S[h].T @ C[t, g * N:(g + 1) * N]
+    want = want.reshape(T, H * V)
+    dx, dB, dC = on_device(x, dtype), on_device(B, dtype), on_device(C, dtype)
+    draw, dbias, drate = on_device(raw, torch.float32), on_device(bias, dtype), on_device(rate, dtype)
+    state = torch.full((3, H, N, V), 7.0, dtype=torch.float32, device=DEV)
+
+    def run(rows, batch):
+        rows = rows.to(DEV)
+        return ops.linear_attention(dC[rows], dB[rows], dx[rows], None, state, batch, H, N, V, dtype,
+                                    step_sizes=(draw[rows].contiguous(), dbias, drate), qk_group=H // groups, raw=True)
+    whole = run(torch.arange(T), Batch([T], slots=[1]))
+    assert whole.dtype == torch.float32
+    assert (whole.double().cpu() - want).abs().max() <= tol * want.abs().max()
+    got = []
+    for at, m in ((0, 1), (1, 2), (3, 64), (67, 1), (68, 82)):
+        rows = torch.cat([torch.arange(at, at + m), torch.arange(5)])
+        res = run(rows, Batch([m, 5], starts=[at, 0], slots=[2, 0]))
+        got.append(res[:m])
+        assert (res[m:].double().cpu() - want[:5]).abs().max() <= tol * want.abs().max()
+    assert (torch.cat(got).double().cpu() - want).abs().max() <= tol * want.abs().max()
+    assert (state[2] - state[1]).abs().max() <= tol * state[1].abs().max()
+    assert (state[1].double().cpu() - S).abs().max() <= tol * S.abs().max()
+
+
 def _paged(rows, page, num_pages, seed):
     """Per-request rows [n, heads, width] scattered into shuffled pages; unused slots hold large
     values, so that reading them shows."""
