@@ -261,28 +261,24 @@ __global__ void joint_norm_kvwrite_kernel(JointNorm p) {
 }
 
 // ------------------------------------------------------------------ gates of a matrix memory with exponential input gate
-// A warp per (request, head) walks the request's tokens 32 at a time.  m_t = max(f_t + m_(t-1), i_t)
-// is a chain of maps x -> max(F + x, I); two such maps compose to another one,
-// (F2, I2) o (F1, I1) = (F1 + F2, max(I1 + F2, I2)), so the 32 tokens are a warp scan.
-__global__ void mlstm_gates_kernel(const float* __restrict__ raw, long long ld, float cap, float* __restrict__ m_state,
-                                   const int* __restrict__ state_slots, const int* __restrict__ fresh,
-                                   const int* __restrict__ cu_q, int num_requests, int H, float* __restrict__ keep,
-                                   float* __restrict__ write, float* __restrict__ floor_) {
-  pdl_trigger();
-  pdl_wait();
+// m_t = max(f_t + m_(t-1), i_t) is a chain of maps x -> max(F + x, I); two such maps compose to another one,
+// (F2, I2) o (F1, I1) = (F1 + F2, max(I1 + F2, I2)), so 32 tokens are a warp scan, and a span of tokens has
+// one map that can be applied before the span's own maximum is known.
+//
+// A warp walks the tokens [a, e) of head h 32 at a time.  EMIT: from the maximum m before token a it writes
+// keep_t, write_t, exp(-m_t) and returns the maximum after the span in .x.  Otherwise it writes nothing and
+// returns the span's map (F, I).
+template <bool EMIT>
+__device__ __forceinline__ float2 mlstm_gates_walk(const float* __restrict__ raw, long long ld, float cap, int H, int h,
+                                                   int a, int e, float m, float* __restrict__ keep,
+                                                   float* __restrict__ write, float* __restrict__ floor_) {
   const int lane = threadIdx.x & 31;
-  const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (pair >= num_requests * H) return;
-  const int b = pair / H, h = pair % H;
-  const int t0 = cu_q[b], t1 = cu_q[b + 1];
-  if (t1 <= t0) return;
-  float* ms = m_state + (size_t)state_slots[b] * H + h;
-  float m = fresh[b] ? 0.f : *ms;
   const float inv_cap = 1.f / cap;
-  for (int base = t0; base < t1; base += 32) {
+  float Fs = 0.f, Is = -INFINITY;
+  for (int base = a; base < e; base += 32) {
     const int t = base + lane;
-    const bool live = t < t1;
-    float gi = -INFINITY, gf = 0.f;
+    const bool live = t < e;
+    float gi = -INFINITY, gf = 0.f;      // (a lane behind the span holds the identity map)
     if (live) {
       gi = cap * tanhf(raw[(size_t)t * ld + h] * inv_cap);
       gf = log_sigmoid_f(cap * tanhf(raw[(size_t)t * ld + H + h] * inv_cap));
@@ -296,18 +292,73 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ raw, long long ld, 
         F = pF + F;
       }
     }
-    const float m_t = fmaxf(F + m, I);
-    float m_prev = __shfl_up_sync(0xffffffffu, m_t, 1);
-    if (lane == 0) m_prev = m;
-    if (live) {
-      keep[(size_t)t * H + h] = expf(gf + m_prev - m_t);
-      write[(size_t)t * H + h] = expf(gi - m_t);
-      floor_[(size_t)t * H + h] = expf(-m_t);
+    if (EMIT) {
+      const float m_t = fmaxf(F + m, I);
+      float m_prev = __shfl_up_sync(0xffffffffu, m_t, 1);
+      if (lane == 0) m_prev = m;
+      if (live) {
+        keep[(size_t)t * H + h] = expf(gf + m_prev - m_t);
+        write[(size_t)t * H + h] = expf(gi - m_t);
+        floor_[(size_t)t * H + h] = expf(-m_t);
+      }
+      m = __shfl_sync(0xffffffffu, m_t, 31);
+    } else {
+      const float tF = __shfl_sync(0xffffffffu, F, 31), tI = __shfl_sync(0xffffffffu, I, 31);
+      Is = fmaxf(Is + tF, tI);
+      Fs += tF;
     }
-    const int last = min(31, t1 - 1 - base);
-    m = __shfl_sync(0xffffffffu, m_t, last);
   }
-  if (lane == 0) *ms = m;
+  return EMIT ? make_float2(m, 0.f) : make_float2(Fs, Is);
+}
+
+// a warp per (request, head): steps of few tokens a request
+__global__ void mlstm_gates_kernel(const float* __restrict__ raw, long long ld, float cap, float* __restrict__ m_state,
+                                   const int* __restrict__ state_slots, const int* __restrict__ fresh,
+                                   const int* __restrict__ cu_q, int num_requests, int H, float* __restrict__ keep,
+                                   float* __restrict__ write, float* __restrict__ floor_) {
+  pdl_trigger();
+  pdl_wait();
+  const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pair >= num_requests * H) return;
+  const int b = pair / H, h = pair % H;
+  const int t0 = cu_q[b], t1 = cu_q[b + 1];
+  if (t1 <= t0) return;
+  float* ms = m_state + (size_t)state_slots[b] * H + h;
+  const float m = mlstm_gates_walk<true>(raw, ld, cap, H, h, t0, t1, fresh[b] ? 0.f : *ms, keep, write, floor_).x;
+  if ((threadIdx.x & 31) == 0) *ms = m;
+}
+
+// a block per (request, head): every warp takes a span of the request's tokens, finds the span's map, learns
+// the maximum before its span from the maps of the spans before it, and walks its span again to write
+__global__ void mlstm_gates_spans_kernel(const float* __restrict__ raw, long long ld, float cap, float* __restrict__ m_state,
+                                         const int* __restrict__ state_slots, const int* __restrict__ fresh,
+                                         const int* __restrict__ cu_q, int H, float* __restrict__ keep,
+                                         float* __restrict__ write, float* __restrict__ floor_) {
+  __shared__ float span_f[32], span_i[32];
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int b = blockIdx.x / H, h = blockIdx.x % H;
+  const int t0 = cu_q[b], t1 = cu_q[b + 1];
+  if (t1 <= t0) return;
+  float* ms = m_state + (size_t)state_slots[b] * H + h;
+  const float m0 = fresh[b] ? 0.f : *ms;
+  const int span = (((t1 - t0) + warps - 1) / warps + 31) / 32 * 32;
+  const int a = min(t1, t0 + warp * span), e = min(t1, a + span);
+  const float2 map = mlstm_gates_walk<false>(raw, ld, cap, H, h, a, e, 0.f, keep, write, floor_);
+  if (lane == 0) {
+    span_f[warp] = map.x;
+    span_i[warp] = map.y;
+  }
+  __syncthreads();          // (also: every thread has read the old maximum before thread 0 writes the new one)
+  float m = m0;
+  for (int w = 0; w < warp; ++w) m = fmaxf(span_f[w] + m, span_i[w]);
+  mlstm_gates_walk<true>(raw, ld, cap, H, h, a, e, m, keep, write, floor_);
+  if (threadIdx.x == 0) {
+    float last = m0;
+    for (int w = 0; w < warps; ++w) last = fmaxf(span_f[w] + last, span_i[w]);
+    *ms = last;
+  }
 }
 
 // ------------------------------------------------------------------ what follows the scan of a matrix memory
@@ -455,10 +506,16 @@ TS_EXPORT int ts_joint_norm_kvwrite(int is_f32, const void* q, long long ldq, co
 }
 
 TS_EXPORT int ts_mlstm_gates(const float* raw, long long ld, float cap, float* m_state, const int* state_slots,
-                             const int* fresh, const int* cu_q, int num_requests, int H, float* keep, float* write,
-                             float* floor_, cudaStream_t stream) {
+                             const int* fresh, const int* cu_q, int num_requests, int max_q_len, int H, float* keep,
+                             float* write, float* floor_, cudaStream_t stream) {
   TS_REQUIRE(num_requests > 0 && H > 0 && cap > 0.f, "mlstm_gates: empty input or a cap that is not positive");
   TS_REQUIRE(raw && m_state && state_slots && fresh && cu_q && keep && write && floor_, "mlstm_gates: a null operand");
+  if (max_q_len >= 128) {
+    const int warps = max_q_len >= 512 ? 16 : (max_q_len + 31) / 32;
+    TS_LAUNCH("mlstm_gates", mlstm_gates_spans_kernel, num_requests * H, warps * 32, 0, stream, raw, ld, cap, m_state,
+              state_slots, fresh, cu_q, H, keep, write, floor_);
+    return 0;
+  }
   const int warps = 4;
   TS_LAUNCH("mlstm_gates", mlstm_gates_kernel, (num_requests * H + warps - 1) / warps, warps * 32, 0, stream, raw, ld, cap,
             m_state, state_slots, fresh, cu_q, num_requests, H, keep, write, floor_);

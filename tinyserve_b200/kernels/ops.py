@@ -1723,7 +1723,8 @@ def mlstm_gates(raw, cap, m_state, ctx, num_heads):
     [T, 2 H]: input-gate logits, then forget-gate logits.  i = cap tanh(. / cap),
     f = logsigmoid(cap tanh(. / cap)), m_t = max(f_t + m_(t-1), i_t) with m in ``m_state`` float32
     [slots, H] (zero for a request that starts).  Returns float32 [T, H] each: keep =
-    exp(f + m_(t-1) - m_t), write = exp(i - m_t), floor = exp(-m_t)."""
+    exp(f + m_(t-1) - m_t), write = exp(i - m_t), floor = exp(-m_t).  Steps with a request of 128 tokens
+    or more (``ctx.max_q_len``) give a block to each (request, head), whose warps take spans of its tokens."""
     _cuda(raw, m_state)
     T, H = raw.shape[0], num_heads
     if raw.dtype != torch.float32 or raw.shape[1] != 2 * H or raw.stride(1) != 1 or m_state.dtype != torch.float32 \
@@ -1732,8 +1733,8 @@ def mlstm_gates(raw, cap, m_state, ctx, num_heads):
     keep, write, floor = (torch.empty(T, H, dtype=torch.float32, device=raw.device) for _ in range(3))
     lib = _sequence()
     _check(lib, lib.ts_mlstm_gates(_ptr(raw), c_longlong(raw.stride(0)), c_float(cap), _ptr(m_state), _ptr(ctx.state_slots),
-                                   _ptr(ctx.fresh), _ptr(ctx.cu_q), c_int(ctx.num_requests), c_int(H), _ptr(keep), _ptr(write),
-                                   _ptr(floor), _stream()))
+                                   _ptr(ctx.fresh), _ptr(ctx.cu_q), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H),
+                                   _ptr(keep), _ptr(write), _ptr(floor), _stream()))
     return keep, write, floor
 
 
