@@ -97,6 +97,8 @@ class ModelSpec:
     embedding_position: PartSpec = None
     # logits <- cap * tanh(logits / cap); 0: none
     logit_softcap: float = 0.0
+    # the embedding rows are multiplied by this on their way into the 32-bit stream
+    embedding_scale: float = 1.0
     # operations on the residual stream between blocks, by name: ((name, PartSpec), ...); a
     # ``LayerCall.before`` says where one runs.  Its tensors live under "{prefix}{name}"
     stream_ops: tuple = ()

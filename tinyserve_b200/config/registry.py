@@ -11,6 +11,7 @@ from __future__ import annotations
 import json
 import os
 
+from .babadra import BabadraConfig
 from .delilorn import DelilornConfig
 from .dudatar import DudatarConfig
 from .model_config import ConfigError, ModelConfig, Qwen3Config
@@ -64,3 +65,4 @@ register_architecture(Qwen3Config.architecture, Qwen3Config)
 register_architecture(DudatarConfig.architecture, DudatarConfig)
 register_architecture(DelilornConfig.architecture, DelilornConfig)
 register_architecture(TarivikConfig.architecture, TarivikConfig)
+register_architecture(BabadraConfig.architecture, BabadraConfig)

@@ -65,6 +65,8 @@ struct MmaAttnParams {
   int chunk;                // > 0: a query at position i sees key j only if i / chunk == j / chunk (no window then)
   const float* slopes;      // [H] or null: slopes[h] * (i - j) is taken off head h's scaled score
   float scale_log2;
+  // a soft cap c > 0 on the scaled score s, c tanh(s / c): cap2 = c log2(e) (0: none), cap_in = scale / c
+  float cap2, cap_in;
   // Decode straight from the fused q/k/v projection (from_qkv != 0; q is not read): every block
   // builds its query rows itself (sum of the split-K partial tiles, per-head RMSNorm, rotary), and
   // the block whose key range holds the newest position builds that key and value too, uses them
@@ -110,6 +112,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// tanh by one exp2 and one division: absolute error of a few 1e-7, which is what a capped score may carry
+__device__ __forceinline__ float soft_tanh(float x) {
+  const float t = fast_exp2(x * (2.f * 1.4426950408889634f));
+  return 1.f - __fdividef(2.f, t + 1.f);       // t = inf gives 1, t = 0 gives -1
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -199,11 +206,12 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[N
 // `keep` are visible besides); a row with pos < 0 sees nothing.
 // MASK false: every key of the tile is visible to both rows (no comparisons).
 // BIAS: row h's score of key j loses sl[h] * (pos[h] - j) (sl in the log2 domain, like the scale).
+// cap2 > 0: the scaled score is capped first, cap2 * tanh(raw score * cap_in) in the log2 domain.
 template <int NT, bool MASK = true, bool BIAS = false>
 __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[D / 8][4], float (&m)[2],
                                              float (&l)[2], const int (&pos)[2], const int (&lo)[2],
                                              int jbase, float scale_log2, int lane, int keep = 0,
-                                             const float* sl = nullptr) {
+                                             const float* sl = nullptr, float cap2 = 0.f, float cap_in = 0.f) {
   const int t = lane & 3;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -214,8 +222,14 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[D / 8
       for (int e = 0; e < 2; ++e) {
         const int j = jbase + nt * 8 + 2 * t + e;
         const bool visible = !MASK || (j <= pos[h] && (j >= lo[h] || j < keep));
-        const float v = !visible ? -INFINITY
-                        : (BIAS ? fmaf(s[nt][2 * h + e], scale_log2, sl[h] * (float)(j - pos[h])) : s[nt][2 * h + e] * scale_log2);
+        float v;
+        if (cap2 > 0.f) {      // (the same for every thread of the launch)
+          v = cap2 * soft_tanh(s[nt][2 * h + e] * cap_in);
+          if (BIAS) v = fmaf(sl[h], (float)(j - pos[h]), v);
+        } else {
+          v = BIAS ? fmaf(s[nt][2 * h + e], scale_log2, sl[h] * (float)(j - pos[h])) : s[nt][2 * h + e] * scale_log2;
+        }
+        if (!visible) v = -INFINITY;
         s[nt][2 * h + e] = v;
         mx = fmaxf(mx, v);
       }
@@ -337,12 +351,12 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams
       qk_tile<BN / 8>(s, my_q, qf, Ks + buf * BN * ROW_BYTES, 0, lane);
       const bool open = tile * BN + BN - 1 <= warp_min_pos && (tile * BN >= warp_max_lo || tile * BN + BN <= keep);
       if (p.slopes) {
-        if (open) softmax_tile<BN / 8, false, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane, 0, sl);
-        else softmax_tile<BN / 8, true, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane, keep, sl);
+        if (open) softmax_tile<BN / 8, false, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane, 0, sl, p.cap2, p.cap_in);
+        else softmax_tile<BN / 8, true, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane, keep, sl, p.cap2, p.cap_in);
       } else if (open) {
-        softmax_tile<BN / 8, false>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane);
+        softmax_tile<BN / 8, false>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane, 0, nullptr, p.cap2, p.cap_in);
       } else {
-        softmax_tile<BN / 8, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane, keep);
+        softmax_tile<BN / 8, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane, keep, nullptr, p.cap2, p.cap_in);
       }
       pv_tile<BN / 8>(o, s, Vs + buf * BN * ROW_BYTES, 0, lane);
     }
@@ -689,8 +703,8 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
     if (jbase < j_hi) {
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       qk_tile<2, TMA>(s, Qs, qf, Ks + buf * KV_TILE, warp * 16, lane);
-      if (p.slopes) softmax_tile<2, true, true>(s, o, m, l, pos, lo, jbase, p.scale_log2, lane, keep, sl);
-      else softmax_tile<2>(s, o, m, l, pos, lo, jbase, p.scale_log2, lane, keep);
+      if (p.slopes) softmax_tile<2, true, true>(s, o, m, l, pos, lo, jbase, p.scale_log2, lane, keep, sl, p.cap2, p.cap_in);
+      else softmax_tile<2>(s, o, m, l, pos, lo, jbase, p.scale_log2, lane, keep, nullptr, p.cap2, p.cap_in);
       pv_tile<2, TMA>(o, s, Vs + buf * KV_TILE, warp * 16, lane);
     }
     __syncthreads();
@@ -876,7 +890,7 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
                                      int num_splits, float* part_o, float* part_ml,
                                      int decode_only, const int* tile_req, const int* tile_q0, int num_tiles,
                                      int tile_queries, int num_pages, int keep_first, const float* sinks,
-                                     int chunk, const float* slopes, cudaStream_t stream) {
+                                     int chunk, const float* slopes, float softcap, cudaStream_t stream) {
   TS_REQUIRE(keep_first >= 0, "paged_attention_mma: keep_first %d", keep_first);
   TS_REQUIRE(chunk >= 0 && (chunk == 0 || window <= 0), "paged_attention_mma: a chunk of %d positions (and no window beside it)", chunk);
   MmaAttnParams extra = {};
@@ -884,6 +898,7 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
   extra.sinks = sinks;
   extra.chunk = chunk;
   extra.slopes = slopes;
+  if (softcap > 0.f) { extra.cap2 = softcap * LOG2E; extra.cap_in = scale / softcap; }
   return paged_attention_mma_impl(&extra, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
                                   num_requests, max_q_len, H, Hkv, page_size, max_blocks, scale, window, num_splits,
                                   part_o, part_ml, decode_only, tile_req, tile_q0, num_tiles,

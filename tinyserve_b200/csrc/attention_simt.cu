@@ -51,6 +51,7 @@ struct AttnParams {
   int chunk;                // > 0: a query at position i sees key j only if i / chunk == j / chunk (no window then)
   const float* slopes;      // [H] or null: slopes[h] * (i - j) is taken off the score of head h
   float scale;
+  float softcap;            // > 0: the scaled score s becomes softcap * tanh(s / softcap) (before the slopes' bias)
 };
 
 template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
@@ -171,6 +172,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(AttnParams 
 #pragma unroll 8
       for (int d = 0; d < D; ++d) s = fmaf(qr[d], kr[d], s);
       s *= p.scale;
+      if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
       const int pos = pos0 + (p.queries_per_tile > 1 ? r / GT : 0);
       const bool visible = j <= pos && j < j_hi && (p.window <= 0 || j > pos - p.window || j < keep) &&
                            (p.chunk <= 0 || j >= pos / p.chunk * p.chunk);
@@ -279,7 +281,7 @@ TS_EXPORT int ts_paged_attention_biased(int dtype, const void* q, void* out, con
                                         int max_q_len, int H, int Hkv, int page_size, int max_blocks,
                                         float scale, int window, int num_splits, float* part_o,
                                         float* part_ml, int keep_first, const float* sinks, int chunk,
-                                        const float* slopes, cudaStream_t stream) {
+                                        const float* slopes, float softcap, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention: empty batch");
   TS_REQUIRE(chunk >= 0 && (chunk == 0 || window <= 0), "paged_attention: a chunk of %d positions (and no window beside it)", chunk);
   TS_REQUIRE(keep_first >= 0, "paged_attention: keep_first %d", keep_first);
@@ -299,7 +301,7 @@ TS_EXPORT int ts_paged_attention_biased(int dtype, const void* q, void* out, con
   p.head_tiles = (G + p.heads_per_tile - 1) / p.heads_per_tile;
   p.num_splits = num_splits; p.window = window; p.scale = scale;
   p.keep_first = keep_first; p.sinks = sinks;
-  p.chunk = chunk; p.slopes = slopes;
+  p.chunk = chunk; p.slopes = slopes; p.softcap = softcap;
   const long long gz = (long long)num_requests * num_splits;
   const long long gy = (long long)Hkv * p.head_tiles;
   TS_REQUIRE(gz <= 65535 && gy <= 65535, "paged_attention: grid too large (%lld requests*splits, %lld head tiles)", gz, gy);
@@ -333,7 +335,7 @@ TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void
                                  float* part_ml, int keep_first, const float* sinks, cudaStream_t stream) {
   return ts_paged_attention_biased(dtype, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens, num_requests,
                                    max_q_len, H, Hkv, page_size, max_blocks, scale, window, num_splits, part_o, part_ml,
-                                   keep_first, sinks, 0, nullptr, stream);
+                                   keep_first, sinks, 0, nullptr, 0.f, stream);
 }
 
 // ------------------------------------------------------------------ no-allocation entry point

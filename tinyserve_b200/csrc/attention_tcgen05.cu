@@ -78,6 +78,8 @@ struct TcAttnParams {
   int chunk;                // > 0: a query at position i sees key j only if i / chunk == j / chunk (no window then)
   const float* slopes;      // [H] or null: slopes[h] * (i - j) is taken off head h's scaled score
   float scale_log2;
+  // a soft cap c > 0 on the scaled score s, c tanh(s / c): cap2 = c log2(e) (0: none), cap_in = scale / c
+  float cap2, cap_in;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -344,7 +346,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tmem_load_wait();
         if (tracer) timeline_mark_thread(21 + 4 * g, t);
         float sc = p.scale_log2;
-        if (biased) {
+        if (p.cap2 > 0.f) {
+          // capped here (tanh by one exp2 and one division), then biased; the scale is spent
+          const float base = slope2 * (float)(j0 - pos);
+#pragma unroll
+          for (int e = 0; e < BN; ++e) {
+            const float t = ex2(sv[e] * p.cap_in * (2.f * 1.4426950408889634f));
+            const float capped = p.cap2 * (1.f - __fdividef(2.f, t + 1.f));
+            sv[e] = biased ? capped + fmaf(slope2, (float)e, base) : capped;
+          }
+          sc = 1.f;
+        } else if (biased) {
           // scaled and biased here, so that the maximum below is the biased scores'; the scale is spent
           const float base = slope2 * (float)(j0 - pos);
 #pragma unroll
@@ -493,7 +505,7 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
                                          int num_pages, int page_size, int max_blocks, float scale, int window,
                                          const int* tile_req, const int* tile_q0, int num_tiles,
                                          int tile_queries, int keep_first, const float* sinks, int chunk,
-                                         const float* slopes, cudaStream_t stream) {
+                                         const float* slopes, float softcap, cudaStream_t stream) {
   TS_REQUIRE(keep_first >= 0, "paged_attention_tcgen05: keep_first %d", keep_first);
   TS_REQUIRE(chunk >= 0 && (chunk == 0 || window <= 0), "paged_attention_tcgen05: a chunk of %d positions (and no window beside it)", chunk);
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_tcgen05: empty batch");
@@ -513,6 +525,8 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.cap2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
   p.heads_per_tile = G < BM ? G : BM;
   p.queries_per_tile = G < BM ? BM / G : 1;
   p.head_tiles = (G + p.heads_per_tile - 1) / p.heads_per_tile;

@@ -212,11 +212,23 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 }
 
 // gated feed-forward: act(gate) * up
-enum { ACT_SILU = 0, ACT_GELU_TANH = 1 };
+enum { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_BOUNDED_SWISH = 2, ACT_COUNT = 3 };
 __device__ __forceinline__ float activate(float g, int act) {
   if (act == ACT_SILU) return g / (1.f + expf(-g));
   const float c = 0.7978845608028654f;
   return 0.5f * g * (1.f + tanhf(c * (g + 0.044715f * g * g * g)));
+}
+// What a gated feed-forward makes of a gate and an up value.  ACT_BOUNDED_SWISH: with
+// g' = min(g, limit) and u' = clamp(u, -limit, limit) it is g' sigmoid(1.702 g') (u' + 1); the
+// other activations are act(g) u and ignore the limit.
+constexpr float BOUNDED_SWISH_SLOPE = 1.702f;
+__device__ __forceinline__ float gated_value(float g, float u, int act, float limit) {
+  if (act == ACT_BOUNDED_SWISH) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-BOUNDED_SWISH_SLOPE * g)) * (u + 1.f);
+  }
+  return activate(g, act) * u;
 }
 
 // a weight vector that is either float or bfloat16, chosen at run time

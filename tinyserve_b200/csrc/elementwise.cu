@@ -14,7 +14,7 @@ TS_DEFINE_LAST_ERROR()
 template <typename T>
 __global__ void embed_lookup_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int n, int vocab,
-                                    const int* __restrict__ slot_tokens) {
+                                    const int* __restrict__ slot_tokens, float scale) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -26,18 +26,18 @@ __global__ void embed_lookup_kernel(const T* __restrict__ table, const int* __re
     return;
   }
   const T* src = table + (size_t)id * n;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = to_f32<T>(src[i]) * scale;
 }
 
 TS_EXPORT int ts_embed_lookup(int dtype, const void* table, const int* ids, float* out,
-                              int num_tokens, int n, int vocab, const int* slot_tokens,
+                              int num_tokens, int n, int vocab, const int* slot_tokens, float scale,
                               cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && n > 0 && vocab > 0, "embed_lookup: empty input");
   const int threads = n >= 1024 ? 256 : 128;
   if (dtype == TS_F32)
-    TS_LAUNCH("embed_lookup", embed_lookup_kernel<float>, num_tokens, threads, 0, stream, (const float*)table, ids, out, n, vocab, slot_tokens);
+    TS_LAUNCH("embed_lookup", embed_lookup_kernel<float>, num_tokens, threads, 0, stream, (const float*)table, ids, out, n, vocab, slot_tokens, scale);
   else if (dtype == TS_BF16)
-    TS_LAUNCH("embed_lookup", embed_lookup_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, n, vocab, slot_tokens);
+    TS_LAUNCH("embed_lookup", embed_lookup_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, n, vocab, slot_tokens, scale);
   else
     return ts_fail("embed_lookup: unknown dtype %d", dtype);
   return 0;
@@ -190,11 +190,13 @@ TS_EXPORT int ts_sanitize_group(int* slot_mapping, int T, long long total_slots,
 // ------------------------------------------------------------------ residual add + RMSNorm
 // One block per output row.  v = residual[r] + x[r] (x may be null), residual[r] = v when
 // `write_residual`, out[i] = v * rsqrt(mean(v^2) + eps) * w.  With `rows`, output row i reads
-// input row rows[i].  The order of the sum depends on n and the block size only.
+// input row rows[i].  The order of the sum depends on n and the block size only.  With `xs` (one
+// factor per column, null: none) x is multiplied by it, in 32-bit, before it is added.
 template <typename T>
 __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ residual,
                                    VecParam w, float eps, T* __restrict__ out,
-                                   const int* __restrict__ rows, int n, int write_residual, PartialSrc ps) {
+                                   const int* __restrict__ rows, int n, int write_residual, PartialSrc ps,
+                                   VecParam xs) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
@@ -205,8 +207,9 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
   float acc = 0.f;
   for (int c = threadIdx.x; c < n; c += blockDim.x) {
     float v = rr[c];
-    if (ps.base) v += ps.load1((int)r, c);
-    else if (xr) v += to_f32<T>(xr[c]);
+    const float s = xs.ptr ? xs[c] : 1.f;
+    if (ps.base) v += ps.load1((int)r, c) * s;
+    else if (xr) v += to_f32<T>(xr[c]) * s;
     acc += v * v;
   }
   const float total = block_sum(acc, scratch);
@@ -214,8 +217,9 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
   T* o = out + (size_t)i * n;
   for (int c = threadIdx.x; c < n; c += blockDim.x) {
     float v = rr[c];
-    if (ps.base) v += ps.load1((int)r, c);
-    else if (xr) v += to_f32<T>(xr[c]);
+    const float s = xs.ptr ? xs[c] : 1.f;
+    if (ps.base) v += ps.load1((int)r, c) * s;
+    else if (xr) v += to_f32<T>(xr[c]) * s;
     if (write_residual) rr[c] = v;
     o[c] = from_f32<T>(v * rstd * w[c]);
   }
@@ -257,7 +261,7 @@ template <> struct Quad<__nv_bfloat16> {
 template <typename T, int ITEMS, int MAX_THREADS = 1024, int MIN_BLOCKS = 1>
 __global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restrict__ residual, VecParam w,
                                        float eps, T* __restrict__ out, const int* __restrict__ rows,
-                                       int n, int write_residual, PartialSrc ps) {
+                                       int n, int write_residual, PartialSrc ps, VecParam xs) {
   __shared__ float scratch[33];
   pdl_trigger();
   // the weights are constants: fetch them while the predecessor still runs (few rows: the
@@ -288,6 +292,13 @@ __global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) add_rmsnorm_vec_kerne
         float xv[4];
         if (ps.base) ps.load4((int)r, c, xv);
         else Quad<T>::load(x + r * n + c, xv);
+        if (xs.ptr) {
+          float sv[4];
+          if (xs.is_f32) Quad<float>::load(static_cast<const float*>(xs.ptr) + c, sv);
+          else Quad<__nv_bfloat16>::load(static_cast<const __nv_bfloat16*>(xs.ptr) + c, sv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) xv[e] *= sv[e];
+        }
 #pragma unroll
         for (int e = 0; e < 4; ++e) v[it][e] += xv[e];
       }
@@ -324,7 +335,8 @@ constexpr int PARTIAL_BATCH = 8;      // loads of partial sums in flight per thr
 template <typename T>
 __global__ void add_rmsnorm_cluster_kernel(const T* __restrict__ x, float* __restrict__ residual, VecParam w,
                                            float eps, T* __restrict__ out, const int* __restrict__ rows,
-                                           int n, int quads_per_block, int write_residual, PartialSrc ps) {
+                                           int n, int quads_per_block, int write_residual, PartialSrc ps,
+                                           VecParam xs) {
   __shared__ float scratch[33];
   __shared__ float cluster_part;
   pdl_trigger();
@@ -332,9 +344,14 @@ __global__ void add_rmsnorm_cluster_kernel(const T* __restrict__ x, float* __res
   const int c = ((int)rank * quads_per_block + (int)threadIdx.x) * 4;
   const bool active = (int)threadIdx.x < quads_per_block && c < n;
   float wv[4] = {0.f, 0.f, 0.f, 0.f};
+  float sv[4] = {1.f, 1.f, 1.f, 1.f};
   if (active) {      // the weights are constants: fetch them while the predecessor still runs
     if (w.is_f32) Quad<float>::load(static_cast<const float*>(w.ptr) + c, wv);
     else Quad<__nv_bfloat16>::load(static_cast<const __nv_bfloat16*>(w.ptr) + c, wv);
+    if (xs.ptr) {
+      if (xs.is_f32) Quad<float>::load(static_cast<const float*>(xs.ptr) + c, sv);
+      else Quad<__nv_bfloat16>::load(static_cast<const __nv_bfloat16*>(xs.ptr) + c, sv);
+    }
   }
   pdl_wait();
   const int i = blockIdx.y;
@@ -345,7 +362,7 @@ __global__ void add_rmsnorm_cluster_kernel(const T* __restrict__ x, float* __res
     Quad<float>::load(residual + r * n + c, v);
     if (ps.base) {
       // all loads of a batch are issued before the first is used; the sum runs in split order
-      float xs[4] = {0.f, 0.f, 0.f, 0.f};
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
       for (int s0 = 0; s0 < ps.splits; s0 += PARTIAL_BATCH) {
         float4 q[PARTIAL_BATCH];
 #pragma unroll
@@ -353,15 +370,15 @@ __global__ void add_rmsnorm_cluster_kernel(const T* __restrict__ x, float* __res
           if (s0 + s < ps.splits) q[s] = __ldcg(reinterpret_cast<const float4*>(ps.base + ps.offset(s0 + s, (int)r, c)));
 #pragma unroll
         for (int s = 0; s < PARTIAL_BATCH; ++s)
-          if (s0 + s < ps.splits) { xs[0] += q[s].x; xs[1] += q[s].y; xs[2] += q[s].z; xs[3] += q[s].w; }
+          if (s0 + s < ps.splits) { sums[0] += q[s].x; sums[1] += q[s].y; sums[2] += q[s].z; sums[3] += q[s].w; }
       }
 #pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] += xs[e];
+      for (int e = 0; e < 4; ++e) v[e] += sums[e] * sv[e];
     } else if (x) {
       float xv[4];
       Quad<T>::load(x + r * n + c, xv);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] += xv[e];
+      for (int e = 0; e < 4; ++e) v[e] += xv[e] * sv[e];
     }
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc += v[e] * v[e];
@@ -387,9 +404,10 @@ __global__ void add_rmsnorm_cluster_kernel(const T* __restrict__ x, float* __res
 
 template <typename T>
 int launch_add_rmsnorm(const void* x, float* residual, VecParam w, float eps, void* out, const int* rows,
-                       int num_out_rows, int n, int write_residual, PartialSrc ps, cudaStream_t stream) {
+                       int num_out_rows, int n, int write_residual, PartialSrc ps, VecParam xs, cudaStream_t stream) {
   const bool aligned = n % 4 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual) |
-                                      reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(w.ptr)) % 16 == 0;
+                                      reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(w.ptr) |
+                                      reinterpret_cast<uintptr_t>(xs.ptr)) % 16 == 0;
   const T* xp = static_cast<const T*>(x);
   T* op = static_cast<T*>(out);
   if (aligned && num_out_rows <= 32 && n >= 1024 && n <= NORM_CLUSTER * 4 * 1024) {
@@ -397,7 +415,7 @@ int launch_add_rmsnorm(const void* x, float* residual, VecParam w, float eps, vo
     const int threads = (quads_per_block + 31) / 32 * 32;
     cudaError_t e = ts_launch_cluster(add_rmsnorm_cluster_kernel<T>, dim3(NORM_CLUSTER, num_out_rows), dim3(threads), 0,
                                       stream, dim3(NORM_CLUSTER), xp, residual, w, eps, op, rows, n, quads_per_block,
-                                      write_residual, ps);
+                                      write_residual, ps, xs);
     if (e != cudaSuccess) return ts_fail("add_rmsnorm: %s", cudaGetErrorString(e));
     return 0;
   }
@@ -408,31 +426,34 @@ int launch_add_rmsnorm(const void* x, float* residual, VecParam w, float eps, vo
     int items = quads <= 1024 ? 1 : (quads <= 2048 ? 2 : 4);
     if (num_out_rows >= 512 && quads >= 256) items = 4;
     int threads = ((quads + items - 1) / items + 31) / 32 * 32;
-    if (items == 1) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 1>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
-    else if (items == 2) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 2>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
-    else if (threads <= 256) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 4, 256, 4>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
-    else TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 4>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
+    if (items == 1) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 1>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps, xs);
+    else if (items == 2) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 2>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps, xs);
+    else if (threads <= 256) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 4, 256, 4>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps, xs);
+    else TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 4>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps, xs);
     return 0;
   }
   const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
-  TS_LAUNCH("add_rmsnorm", add_rmsnorm_kernel<T>, num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
+  TS_LAUNCH("add_rmsnorm", add_rmsnorm_kernel<T>, num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps, xs);
   return 0;
 }
 
 // With `partials` (split-K partial tiles of a product [M, n], see PartialSrc) x is their sum.
+// `x_scale` (n factors, or null): x times it is what is added.
 TS_EXPORT int ts_add_rmsnorm(int dtype, const void* x, float* residual, const void* weight,
                              int weight_is_f32, float eps, void* out, const int* rows,
                              int num_out_rows, int n, int write_residual, const float* partials,
-                             int splits, int n_tiles, int t_tiles, int tile_t, cudaStream_t stream) {
+                             int splits, int n_tiles, int t_tiles, int tile_t, const void* x_scale,
+                             int x_scale_is_f32, cudaStream_t stream) {
   TS_REQUIRE(num_out_rows > 0 && n > 0, "add_rmsnorm: empty input");
   TS_REQUIRE(partials == nullptr || (x == nullptr && splits > 0 && n_tiles * 128 >= n && tile_t > 0),
              "add_rmsnorm: partial tiles do not fit the row length");
   PartialSrc ps{partials, splits, n_tiles, t_tiles, tile_t};
   VecParam w{weight, weight_is_f32};
+  VecParam xs{x_scale, x_scale_is_f32};
   if (dtype == TS_F32)
-    return launch_add_rmsnorm<float>(x, residual, w, eps, out, rows, num_out_rows, n, write_residual, ps, stream);
+    return launch_add_rmsnorm<float>(x, residual, w, eps, out, rows, num_out_rows, n, write_residual, ps, xs, stream);
   if (dtype == TS_BF16)
-    return launch_add_rmsnorm<__nv_bfloat16>(x, residual, w, eps, out, rows, num_out_rows, n, write_residual, ps, stream);
+    return launch_add_rmsnorm<__nv_bfloat16>(x, residual, w, eps, out, rows, num_out_rows, n, write_residual, ps, xs, stream);
   return ts_fail("add_rmsnorm: unknown dtype %d", dtype);
 }
 
@@ -513,7 +534,7 @@ TS_EXPORT int ts_reduce_partials(int dtype, const float* partials, int splits, i
 }
 
 // ------------------------------------------------------------------ gated activation
-// in [rows, 2 * inter] -> out [rows, inter] = act(gate) * up.  block == 0: in = gate | up (two
+// in [rows, 2 * inter] -> out [rows, inter] = act(gate) * up (gated_value).  block == 0: in = gate | up (two
 // halves); block > 0: gate and up alternate in blocks of that many columns (gate columns
 // [0, block), up columns [0, block), gate columns [block, 2 block), ...), the layout of a fused
 // projection whose weight rows are interleaved so that one 128-row tile of the tcgen05 product
@@ -522,7 +543,7 @@ __device__ __forceinline__ int gate_column(int c, int block) { return block ? (c
 
 template <typename T>
 __global__ void gated_activation_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
-                                        int act, int block) {
+                                        int act, int block, float limit) {
   pdl_trigger();
   pdl_wait();
   const size_t row = blockIdx.x;
@@ -530,13 +551,13 @@ __global__ void gated_activation_kernel(const T* __restrict__ in, T* __restrict_
   if (c >= inter) return;
   const T* r = in + row * 2 * inter;
   const int g = gate_column(c, block), u = g + (block ? block : inter);
-  out[row * inter + c] = from_f32<T>(activate(to_f32<T>(r[g]), act) * to_f32<T>(r[u]));
+  out[row * inter + c] = from_f32<T>(gated_value(to_f32<T>(r[g]), to_f32<T>(r[u]), act, limit));
 }
 
 // 16 bytes per thread and operand, for widths that are a multiple of 16 / sizeof(T)
 template <typename T>
 __global__ void gated_activation_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int act,
-                                            int block) {
+                                            int block, float limit) {
   constexpr int V = 16 / sizeof(T);
   pdl_trigger();
   pdl_wait();
@@ -555,7 +576,7 @@ __global__ void gated_activation_vec_kernel(const T* __restrict__ in, T* __restr
     for (int e = 0; e < 4; ++e) { g[4 * h + e] = a[e]; u[4 * h + e] = b[e]; }
   }
 #pragma unroll
-  for (int e = 0; e < V; ++e) o[e] = activate(g[e], act) * u[e];
+  for (int e = 0; e < V; ++e) o[e] = gated_value(g[e], u[e], act, limit);
 #pragma unroll
   for (int h = 0; h < V / 4; ++h) {
     float a[4] = {o[4 * h], o[4 * h + 1], o[4 * h + 2], o[4 * h + 3]};
@@ -564,29 +585,30 @@ __global__ void gated_activation_vec_kernel(const T* __restrict__ in, T* __restr
 }
 
 template <typename T>
-int launch_gated_activation(const void* in, void* out, int num_rows, int inter, int act, int block,
+int launch_gated_activation(const void* in, void* out, int num_rows, int inter, int act, int block, float limit,
                             cudaStream_t stream) {
   constexpr int V = 16 / sizeof(T);
   const bool vec = inter % V == 0 && block % V == 0 &&
                    (reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
   if (vec) {
     dim3 grid(num_rows, (inter / V + 255) / 256);
-    TS_LAUNCH("gated_activation", gated_activation_vec_kernel<T>, grid, 256, 0, stream, (const T*)in, (T*)out, inter, act, block);
+    TS_LAUNCH("gated_activation", gated_activation_vec_kernel<T>, grid, 256, 0, stream, (const T*)in, (T*)out, inter, act, block, limit);
   } else {
     dim3 grid(num_rows, (inter + 255) / 256);
-    TS_LAUNCH("gated_activation", gated_activation_kernel<T>, grid, 256, 0, stream, (const T*)in, (T*)out, inter, act, block);
+    TS_LAUNCH("gated_activation", gated_activation_kernel<T>, grid, 256, 0, stream, (const T*)in, (T*)out, inter, act, block, limit);
   }
   return 0;
 }
 
 TS_EXPORT int ts_gated_activation(int dtype, const void* in, void* out, int num_rows, int inter,
-                                  int act, int block, cudaStream_t stream) {
+                                  int act, int block, float limit, cudaStream_t stream) {
   TS_REQUIRE(num_rows > 0 && inter > 0, "gated_activation: empty input");
   TS_REQUIRE(block >= 0 && (block == 0 || inter % block == 0), "gated_activation: %d columns do not come in blocks of %d", inter, block);
   TS_REQUIRE((inter + 255) / 256 <= 65535, "gated_activation: width %d is too large", inter);
-  TS_REQUIRE(act == ACT_SILU || act == ACT_GELU_TANH, "gated_activation: unknown activation %d", act);
-  if (dtype == TS_F32) return launch_gated_activation<float>(in, out, num_rows, inter, act, block, stream);
-  if (dtype == TS_BF16) return launch_gated_activation<__nv_bfloat16>(in, out, num_rows, inter, act, block, stream);
+  TS_REQUIRE(act >= 0 && act < ACT_COUNT, "gated_activation: unknown activation %d", act);
+  TS_REQUIRE(act != ACT_BOUNDED_SWISH || limit > 0.f, "gated_activation: the bound must be positive");
+  if (dtype == TS_F32) return launch_gated_activation<float>(in, out, num_rows, inter, act, block, limit, stream);
+  if (dtype == TS_BF16) return launch_gated_activation<__nv_bfloat16>(in, out, num_rows, inter, act, block, limit, stream);
   return ts_fail("gated_activation: unknown dtype %d", dtype);
 }
 
@@ -1212,6 +1234,41 @@ TS_EXPORT int ts_softcap(float* x, long long count, float cap, cudaStream_t stre
   return 0;
 }
 
+// ------------------------------------------------------------------ addends taken into the 32-bit stream
+// residual += x * xs (x stored as T, xs one factor per column; either may be null) + first (32-bit
+// rows, or null): what a block left pending, and the stream as it left the embedding, both added
+// before a group of layers runs again.
+template <typename T>
+__global__ void stream_add_kernel(float* __restrict__ residual, const T* __restrict__ x, PartialSrc ps, VecParam xs,
+                                  const float* __restrict__ first, int n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t m = blockIdx.x;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float v = residual[m * n + c];
+    const float s = xs.ptr ? xs[c] : 1.f;
+    if (ps.base) v += ps.load1((int)m, c) * s;
+    else if (x) v += to_f32<T>(x[m * n + c]) * s;
+    if (first) v += first[m * n + c];
+    residual[m * n + c] = v;
+  }
+}
+
+TS_EXPORT int ts_stream_add(int dtype, float* residual, const void* x, const void* x_scale, int x_scale_is_f32,
+                            const float* first, int num_rows, int n, const float* partials, int splits, int n_tiles,
+                            int t_tiles, int tile_t, cudaStream_t stream) {
+  TS_REQUIRE(num_rows > 0 && n > 0, "stream_add: empty input");
+  TS_REQUIRE(partials == nullptr || (x == nullptr && splits > 0 && n_tiles * 128 >= n && tile_t > 0),
+             "stream_add: partial tiles do not fit the row length");
+  PartialSrc ps{partials, splits, n_tiles, t_tiles, tile_t};
+  VecParam xs{x_scale, x_scale_is_f32};
+  const int threads = n >= 512 ? 256 : 128;
+  if (dtype == TS_F32) TS_LAUNCH("stream_add", stream_add_kernel<float>, num_rows, threads, 0, stream, residual, (const float*)x, ps, xs, first, n);
+  else if (dtype == TS_BF16) TS_LAUNCH("stream_add", stream_add_kernel<__nv_bfloat16>, num_rows, threads, 0, stream, residual, (const __nv_bfloat16*)x, ps, xs, first, n);
+  else return ts_fail("stream_add: unknown dtype %d", dtype);
+  return 0;
+}
+
 // ------------------------------------------------------------------ a vector added to every row (32-bit rows)
 __global__ void add_row_vector_kernel(float* __restrict__ x, VecParam v, int n) {
   pdl_trigger();
@@ -1323,13 +1380,21 @@ TS_EXPORT int ts_mean_of_normed(int dtype, int count, const void* const* xs, con
 //   v heads: copied to the value page, [vdim, D) zero.
 // D >= max(dim, vdim) is the head size of the attention kernel: zero key columns add nothing to
 // a score and zero value columns give output columns that the caller drops.
+// With `qw` / `kw` (dim weights each, null: none) every q and k head is first divided by its root
+// mean square over dim (pre_eps inside the root) and multiplied by the weight, before the rotation.
+// `maps` M > 1: every head has M score maps over the same values.  q then holds H = heads * M rows
+// laid out [head][map], k holds G = kv heads * M rows laid out [kv head][map] and v holds G / M
+// heads.  The attention kernels see H query heads on G key/value heads; since they give query
+// head i the key/value head i / (H / G), a head's maps are stored apart: map m of head h, which
+// belongs to kv head g = h / r (r heads per kv head), goes to query row g M r + m r + h % r, which
+// is served by key/value head g M + m: the key of (g, m) beside a copy of the value of g.
 template <typename T>
 __global__ void rope_unit_kvwrite_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, long long ldk,
                                          const T* __restrict__ v, long long ldv, T* __restrict__ q_out,
                                          const int* __restrict__ positions, RopeArgs rope, int unit_norm, float eps,
                                          int H, int G, int dim, int vdim, int D, T* __restrict__ k_cache,
                                          T* __restrict__ v_cache, const int* __restrict__ slot_mapping, int page_size,
-                                         int heads_total) {
+                                         int heads_total, VecParam qw, VecParam kw, float pre_eps, int maps) {
   pdl_trigger();
   pdl_wait();
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1341,28 +1406,49 @@ __global__ void rope_unit_kvwrite_kernel(const T* __restrict__ q, long long ldq,
     bool is_v = false;
     if (head < H) {
       src = q + (size_t)t * ldq + (size_t)head * dim;
-      dst = q_out + ((size_t)t * H + head) * D;
+      int row = head;
+      if (maps > 1) {
+        const int h = head / maps, m = head % maps, r = H / G;      // r: heads per kv head (H / maps over G / maps)
+        row = (h / r) * maps * r + m * r + h % r;
+      }
+      dst = q_out + ((size_t)t * H + row) * D;
     } else {
       const int slot = slot_mapping[t];
       if (slot < 0) continue;
       is_v = head >= H + G;
       const int g = is_v ? head - H - G : head - H;
       const size_t page = slot / page_size, in_page = slot % page_size;
-      src = is_v ? v + (size_t)t * ldv + (size_t)g * vdim : k + (size_t)t * ldk + (size_t)g * dim;
-      dst = (is_v ? v_cache : k_cache) + ((page * G + g) * page_size + in_page) * D;
-    }
-    if (is_v) {
-      for (int i = lane; i < D; i += 32) dst[i] = i < vdim ? src[i] : from_f32<T>(0.f);
-      continue;
+      if (is_v) {
+        // the value head, once for every map's key/value head
+        src = v + (size_t)t * ldv + (size_t)g * vdim;
+        for (int m = 0; m < maps; ++m) {
+          dst = v_cache + ((page * G + g * maps + m) * page_size + in_page) * D;
+          for (int i = lane; i < D; i += 32) dst[i] = i < vdim ? src[i] : from_f32<T>(0.f);
+        }
+        continue;
+      }
+      src = k + (size_t)t * ldk + (size_t)g * dim;
+      dst = k_cache + ((page * G + g) * page_size + in_page) * D;
     }
     const int pos = positions[t];
+    const VecParam w = head < H ? qw : kw;
+    float pre = 1.f;
+    if (w.ptr) {
+      float acc = 0.f;
+      for (int i = lane; i < dim; i += 32) {
+        const float a = to_f32<T>(src[i]);
+        acc += a * a;
+      }
+      pre = rsqrtf(warp_sum(acc) / (float)dim + pre_eps);
+    }
+    auto element = [&](int i) { return w.ptr ? to_f32<T>(src[i]) * pre * w[i] : to_f32<T>(src[i]); };
     auto rotated = [&](int i) {
-      const float a = to_f32<T>(src[i]);
+      const float a = element(i);
       if (i >= R) return a;
       const int j = rope.interleaved ? i >> 1 : (i < half ? i : i - half);
       const bool first = rope.interleaved ? !(i & 1) : i < half;
       const int mate = rope.interleaved ? i ^ 1 : (first ? i + half : i - half);
-      const float b = to_f32<T>(src[mate]);
+      const float b = element(mate);
       const float c = rope.cos[(size_t)pos * half + j], s = rope.sin[(size_t)pos * half + j];
       return first ? a * c - b * s : a * c + b * s;
     };
@@ -1383,26 +1469,30 @@ TS_EXPORT int ts_rope_unit_kvwrite(int dtype, const void* q, long long ldq, cons
                                    long long ldv, void* q_out, const int* positions, const float* cos, const float* sin,
                                    int rotary_dim, int interleaved, int unit_norm, float eps, int num_tokens, int H, int G,
                                    int dim, int vdim, int D, void* k_cache, void* v_cache, const int* slot_mapping,
-                                   int page_size, cudaStream_t stream) {
+                                   int page_size, const void* q_weight, const void* k_weight, int weights_are_f32,
+                                   float pre_eps, int maps, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && H > 0 && G > 0 && dim > 0 && vdim > 0 && D >= dim && D >= vdim,
              "rope_unit_kvwrite: sizes do not fit (dim %d, vdim %d, stored head size %d)", dim, vdim, D);
+  TS_REQUIRE(maps >= 1 && H % maps == 0 && G % maps == 0 && H % G == 0, "rope_unit_kvwrite: %d maps do not divide %d and %d heads", maps, H, G);
+  TS_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "rope_unit_kvwrite: q and k are normed together or not at all");
   TS_REQUIRE(rotary_dim >= 0 && rotary_dim <= dim && rotary_dim % 2 == 0,
              "rope_unit_kvwrite: rotary_dim %d does not fit head size %d", rotary_dim, dim);
   TS_REQUIRE(rotary_dim == 0 || (cos && sin), "rope_unit_kvwrite: rotary without tables");
   TS_REQUIRE(slot_mapping == nullptr || (k_cache && v_cache && page_size > 0), "rope_unit_kvwrite: cache write without a cache");
-  const int heads_total = slot_mapping ? H + 2 * G : H;
+  const int heads_total = slot_mapping ? H + G + G / maps : H;
   const int warps = num_tokens >= 256 ? 8 : 4;
   dim3 grid(num_tokens, num_tokens >= 256 ? 1 : (heads_total + warps - 1) / warps);
   RopeArgs rope{cos, sin, rotary_dim, interleaved};
+  const VecParam qw{q_weight, weights_are_f32}, kw{k_weight, weights_are_f32};
   if (dtype == TS_F32)
     TS_LAUNCH("rope_unit_kvwrite", rope_unit_kvwrite_kernel<float>, grid, warps * 32, 0, stream, (const float*)q, ldq,
               (const float*)k, ldk, (const float*)v, ldv, (float*)q_out, positions, rope, unit_norm, eps, H, G, dim, vdim, D,
-              (float*)k_cache, (float*)v_cache, slot_mapping, page_size, heads_total);
+              (float*)k_cache, (float*)v_cache, slot_mapping, page_size, heads_total, qw, kw, pre_eps, maps);
   else if (dtype == TS_BF16)
     TS_LAUNCH("rope_unit_kvwrite", rope_unit_kvwrite_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream,
               (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k, ldk, (const __nv_bfloat16*)v, ldv,
               (__nv_bfloat16*)q_out, positions, rope, unit_norm, eps, H, G, dim, vdim, D, (__nv_bfloat16*)k_cache,
-              (__nv_bfloat16*)v_cache, slot_mapping, page_size, heads_total);
+              (__nv_bfloat16*)v_cache, slot_mapping, page_size, heads_total, qw, kw, pre_eps, maps);
   else
     return ts_fail("rope_unit_kvwrite: unknown dtype %d", dtype);
   return 0;
@@ -1431,5 +1521,47 @@ TS_EXPORT int ts_head_gate(int dtype, const void* attn, const void* gate, long l
   if (dtype == TS_F32) TS_LAUNCH("head_gate", head_gate_kernel<float>, num_tokens, threads, 0, stream, (const float*)attn, (const float*)gate, ldg, (float*)out, H, D, vdim);
   else if (dtype == TS_BF16) TS_LAUNCH("head_gate", head_gate_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, H, D, vdim);
   else return ts_fail("head_gate: unknown dtype %d", dtype);
+  return 0;
+}
+
+// ------------------------------------------------------------------ difference of two score maps
+// attn [T, 2 heads, D] holds, per head, the outputs of two score maps over the same values, in the
+// row order that rope_unit_kvwrite gives the maps (map m of head h at row g 2 r + m r + h % r,
+// g = h / r, r heads per kv head).  out [T, heads * vdim]: d = a_0 - lambda a_1 over the first vdim
+// columns, then d / sqrt(mean(d^2) + eps) * post.  One warp per (token, head), 32-bit.
+template <typename T>
+__global__ void map_difference_kernel(const T* __restrict__ attn, T* __restrict__ out, int heads, int r, int D, int vdim,
+                                      float lambda, float eps, float post, int num_tokens) {
+  pdl_trigger();
+  pdl_wait();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * warps + warp;
+  if (item >= (long long)num_tokens * heads) return;
+  const size_t t = item / heads;
+  const int h = (int)(item % heads);
+  const int row = (h / r) * 2 * r + h % r;
+  const T* a0 = attn + (t * 2 * heads + row) * D;
+  const T* a1 = a0 + (size_t)r * D;
+  float acc = 0.f;
+  for (int c = lane; c < vdim; c += 32) {
+    const float d = to_f32<T>(a0[c]) - lambda * to_f32<T>(a1[c]);
+    acc += d * d;
+  }
+  const float f = rsqrtf(warp_sum(acc) / (float)vdim + eps) * post;
+  T* o = out + (t * heads + h) * vdim;
+  for (int c = lane; c < vdim; c += 32) o[c] = from_f32<T>((to_f32<T>(a0[c]) - lambda * to_f32<T>(a1[c])) * f);
+}
+
+TS_EXPORT int ts_map_difference(int dtype, const void* attn, void* out, int num_tokens, int heads, int kv_heads, int D,
+                                int vdim, float lambda, float eps, float post, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && vdim > 0 && D >= vdim,
+             "map_difference: sizes do not fit");
+  const int warps = 4;
+  const long long items = (long long)num_tokens * heads;
+  const int blocks = (int)((items + warps - 1) / warps);
+  const int r = heads / kv_heads;
+  if (dtype == TS_F32) TS_LAUNCH("map_difference", map_difference_kernel<float>, blocks, warps * 32, 0, stream, (const float*)attn, (float*)out, heads, r, D, vdim, lambda, eps, post, num_tokens);
+  else if (dtype == TS_BF16) TS_LAUNCH("map_difference", map_difference_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (const __nv_bfloat16*)attn, (__nv_bfloat16*)out, heads, r, D, vdim, lambda, eps, post, num_tokens);
+  else return ts_fail("map_difference: unknown dtype %d", dtype);
   return 0;
 }

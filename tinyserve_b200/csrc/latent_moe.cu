@@ -11,12 +11,13 @@
 //    the latent space followed by its rotated part, padded with zeros to the stored width.
 //  * ts_gate_heads: out[t, h, :] = x[h, t, :] * sigmoid(gate[t, h, :]).
 //  * ts_moe_route: softmax over all experts of a token's router logits; the `top` largest keep
-//    their probability (not renormalised), the others get zero.
+//    their probability (as it is, or with `renorm` divided by the sum of the kept ones, which is the
+//    softmax over the chosen logits alone), the others get zero.
 //  * ts_moe_activate: a[t, e, :] <- act(a[t, e, :]) * gate[t, e], act = relu squared.
 //  * ts_moe_route_scored: scores s = sigmoid(z); the choice is made on s + correction, among the
 //    experts of the `keep` best of `groups` equal groups of neighbours (a group's score: the sum of
 //    its two largest choice scores); the `top` chosen experts keep s as their weight.
-//  * ts_moe_gated_activate: out[t, e, :] = silu(a[t, e, :ff]) * a[t, e, ff:] * gate[t, e].
+//  * ts_moe_gated_activate: out[t, e, :] = gated_value(a[t, e, :ff], a[t, e, ff:]) * gate[t, e].
 //  * ts_moe_group, ts_moe_gather, ts_moe_combine: the tokens of a step sorted by expert (every
 //    expert's rows a run that starts at a multiple of 16), their inputs gathered into that order,
 //    and the experts' outputs added back per token with the router's weights in 32-bit.
@@ -63,6 +64,7 @@ struct LatentPrepare {
   const void* proj; long long ld;         // [T, >= q_rank + kv_rank + rot_dim]: query latent | kv latent | shared key part
   int q_rank, kv_rank, rot_dim, stored;   // stored: width of a cache row, >= kv_rank + rot_dim
   int has_kv;                             // 0: the projection holds the query latent only
+  int interleaved;                        // pairs (2j, 2j + 1) instead of (j, j + rot_dim / 2)
   VecParam q_weight, kv_weight;
   float eps;
   const int* positions; const float* cos; const float* sin;   // tables [positions, rot_dim / 2]
@@ -100,21 +102,23 @@ __global__ void latent_prepare_kernel(LatentPrepare p) {
   const int half = p.rot_dim >> 1;
   const size_t at = (size_t)p.positions[t] * half;
   for (int j = threadIdx.x; j < half; j += blockDim.x) {
-    const float a = to_f32<T>(kv[p.kv_rank + j]), b = to_f32<T>(kv[p.kv_rank + j + half]);
+    const int ia = p.kv_rank + (p.interleaved ? 2 * j : j), ib = p.kv_rank + (p.interleaved ? 2 * j + 1 : j + half);
+    const float a = to_f32<T>(kv[ia]), b = to_f32<T>(kv[ib]);
     const float cs = p.cos[at + j], sn = p.sin[at + j];
-    dst[p.kv_rank + j] = from_f32<T>(a * cs - b * sn);
-    dst[p.kv_rank + j + half] = from_f32<T>(b * cs + a * sn);
+    dst[ia] = from_f32<T>(a * cs - b * sn);
+    dst[ib] = from_f32<T>(b * cs + a * sn);
   }
   for (int c = p.kv_rank + p.rot_dim + threadIdx.x; c < p.stored; c += blockDim.x) dst[c] = from_f32<T>(0.f);
 }
 
 // ------------------------------------------------------------------ latent attention: query rows
-// out[t, h, :] = [ carried[h, t, :kv_rank] | rotate(q[t, h, dim : dim + rot_dim]) | 0 ]
+// out[t, h, :] = [ carried[h, t, :kv_rank] | rotate(q[t, h, dim : dim + rot_dim]) | 0 ]; the rotation pairs
+// element j with j + rot_dim / 2, or with `interleaved` element 2j with 2j + 1
 template <typename T>
 __global__ void latent_query_kernel(const T* __restrict__ carried, const T* __restrict__ q, long long ldq, int H, int dim,
                                     int rot_dim, int kv_rank, int stored, const int* __restrict__ positions,
                                     const float* __restrict__ cos, const float* __restrict__ sin, T* __restrict__ out,
-                                    int num_tokens) {
+                                    int num_tokens, int interleaved) {
   pdl_trigger();
   pdl_wait();
   const size_t t = blockIdx.x;
@@ -126,16 +130,17 @@ __global__ void latent_query_kernel(const T* __restrict__ carried, const T* __re
     for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) dst[c] = src[c];
     const T* qr = q + t * ldq + (size_t)h * (dim + rot_dim) + dim;
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
-      const float a = to_f32<T>(qr[j]), b = to_f32<T>(qr[j + half]);
+      const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
+      const float a = to_f32<T>(qr[ia]), b = to_f32<T>(qr[ib]);
       const float cs = cos[at + j], sn = sin[at + j];
-      dst[kv_rank + j] = from_f32<T>(a * cs - b * sn);
-      dst[kv_rank + j + half] = from_f32<T>(b * cs + a * sn);
+      dst[kv_rank + ia] = from_f32<T>(a * cs - b * sn);
+      dst[kv_rank + ib] = from_f32<T>(b * cs + a * sn);
     }
     for (int c = kv_rank + rot_dim + threadIdx.x; c < stored; c += blockDim.x) dst[c] = from_f32<T>(0.f);
   }
 }
 
-// out[t, h * n + c] = x[h, t, c] * sigmoid(gate[t * ldg + h * n + c])
+// out[t, h * n + c] = x[h, t, c] * sigmoid(gate[t * ldg + h * n + c]) (gate null: the heads are only laid side by side)
 template <typename T>
 __global__ void gate_heads_kernel(const T* __restrict__ x, const T* __restrict__ gate, long long ldg, T* __restrict__ out,
                                   int H, int n, int num_tokens) {
@@ -144,15 +149,16 @@ __global__ void gate_heads_kernel(const T* __restrict__ x, const T* __restrict__
   const size_t t = blockIdx.x;
   for (int i = threadIdx.x; i < H * n; i += blockDim.x) {
     const int h = i / n, c = i % n;
-    const float g = to_f32<T>(gate[t * ldg + i]);
-    out[t * H * n + i] = from_f32<T>(to_f32<T>(x[((size_t)h * num_tokens + t) * n + c]) / (1.f + expf(-g)));
+    const T v = x[((size_t)h * num_tokens + t) * n + c];
+    out[t * H * n + i] = gate ? from_f32<T>(to_f32<T>(v) / (1.f + expf(-to_f32<T>(gate[t * ldg + i])))) : v;
   }
 }
 
 // ------------------------------------------------------------------ mixture of experts
 // a warp per token: probabilities of all experts, the `top` largest kept (ties: the lower number)
 // one warp, one token: z [E] logits -> g [E] (global or shared memory)
-__device__ __forceinline__ void route_token(const float* __restrict__ z, float* g, int E, int top, int lane) {
+__device__ __forceinline__ void route_token(const float* __restrict__ z, float* g, int E, int top, int lane,
+                                            int renorm = 0) {
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
   mx = warp_max(mx);
@@ -180,6 +186,14 @@ __device__ __forceinline__ void route_token(const float* __restrict__ z, float* 
   }
   for (int e = lane; e < E; e += 32)
     if (g[e] < 0.f) g[e] = 0.f;
+  if (renorm) {      // the softmax over the chosen logits alone: their probabilities over their own sum
+    __syncwarp();
+    float chosen = 0.f;
+    for (int e = lane; e < E; e += 32) chosen += g[e];
+    chosen = warp_sum(chosen);
+    const float r = 1.f / chosen;
+    for (int e = lane; e < E; e += 32) g[e] *= r;
+  }
 }
 
 // One warp, one token.  z [E] logits, corr [E] or null -> g [E]: sigmoid(z) for the chosen experts,
@@ -263,10 +277,10 @@ __global__ void moe_route_scored_kernel(const float* __restrict__ logits, const 
                      top, groups, keep, lane);
 }
 
-// out[r, e * ff + j] = silu(a[r, e * 2 ff + j]) * a[r, e * 2 ff + ff + j] * gates[r, e] (gates null: 1)
+// out[r, e * ff + j] = gated_value(a[r, e * 2 ff + j], a[r, e * 2 ff + ff + j]) * gates[r, e] (gates null: 1)
 template <typename T>
 __global__ void moe_gated_activate_kernel(const T* __restrict__ a, const float* __restrict__ gates, int E, int ff,
-                                          T* __restrict__ out) {
+                                          T* __restrict__ out, int act, float limit) {
   pdl_trigger();
   pdl_wait();
   const size_t r = blockIdx.x;
@@ -278,19 +292,20 @@ __global__ void moe_gated_activate_kernel(const T* __restrict__ a, const float* 
     float y = 0.f;
     if (g != 0.f) {
       const float gate = to_f32<T>(row[(size_t)e * 2 * ff + j]), up = to_f32<T>(row[(size_t)e * 2 * ff + ff + j]);
-      y = gate / (1.f + expf(-gate)) * up * g;
+      y = gated_value(gate, up, act, limit) * g;
     }
     dst[i] = from_f32<T>(y);
   }
 }
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, float* __restrict__ gates, int num_tokens, int E, int top) {
+__global__ void moe_route_kernel(const float* __restrict__ logits, float* __restrict__ gates, int num_tokens, int E, int top,
+                                 int renorm) {
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + warp;
   if (t >= num_tokens) return;
-  route_token(logits + (size_t)t * E, gates + (size_t)t * E, E, top, lane);
+  route_token(logits + (size_t)t * E, gates + (size_t)t * E, E, top, lane, renorm);
 }
 
 // 16 bytes of a row as floats and back
@@ -524,12 +539,13 @@ TS_EXPORT int ts_normed_add_rmsnorm(int dtype, const void* y, const void* w_post
 TS_EXPORT int ts_latent_prepare(int dtype, const void* proj, long long ld, int q_rank, int kv_rank, int rot_dim, int stored,
                                 int has_kv, const void* q_weight, int q_weight_is_f32, const void* kv_weight,
                                 int kv_weight_is_f32, float eps, const int* positions, const float* cos, const float* sin,
-                                void* q_latent, void* cache, const int* slot_mapping, int num_tokens, cudaStream_t stream) {
+                                void* q_latent, void* cache, const int* slot_mapping, int num_tokens, int interleaved,
+                                cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && q_rank > 0 && proj && q_weight && q_latent, "latent_prepare: empty input");
   TS_REQUIRE(!has_kv || (kv_rank > 0 && rot_dim >= 0 && rot_dim % 2 == 0 && stored >= kv_rank + rot_dim && kv_weight),
              "latent_prepare: a latent of %d with a rotated part of %d does not fit rows of %d", kv_rank, rot_dim, stored);
   TS_REQUIRE(!has_kv || rot_dim == 0 || (positions && cos && sin), "latent_prepare: rotation without tables");
-  LatentPrepare p{proj, ld, q_rank, kv_rank, rot_dim, stored, has_kv, VecParam{q_weight, q_weight_is_f32},
+  LatentPrepare p{proj, ld, q_rank, kv_rank, rot_dim, stored, has_kv, interleaved, VecParam{q_weight, q_weight_is_f32},
                   VecParam{kv_weight, kv_weight_is_f32}, eps, positions, cos, sin, q_latent, cache,
                   cache ? slot_mapping : nullptr};
   const int widest = q_rank > kv_rank ? q_rank : kv_rank;
@@ -542,24 +558,25 @@ TS_EXPORT int ts_latent_prepare(int dtype, const void* proj, long long ld, int q
 
 TS_EXPORT int ts_latent_query(int dtype, const void* carried, const void* q, long long ldq, int H, int dim, int rot_dim,
                               int kv_rank, int stored, const int* positions, const float* cos, const float* sin, void* out,
-                              int num_tokens, cudaStream_t stream) {
+                              int num_tokens, int interleaved, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && H > 0 && kv_rank > 0 && stored >= kv_rank + rot_dim && rot_dim % 2 == 0 && carried && q && out,
              "latent_query: sizes do not fit");
   TS_REQUIRE(rot_dim == 0 || (positions && cos && sin), "latent_query: rotation without tables");
   dim3 grid(num_tokens, H < 16 ? H : 16);
   if (dtype == TS_F32)
     TS_LAUNCH("latent_query", latent_query_kernel<float>, grid, 128, 0, stream, (const float*)carried, (const float*)q, ldq, H, dim,
-              rot_dim, kv_rank, stored, positions, cos, sin, (float*)out, num_tokens);
+              rot_dim, kv_rank, stored, positions, cos, sin, (float*)out, num_tokens, interleaved);
   else if (dtype == TS_BF16)
     TS_LAUNCH("latent_query", latent_query_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)carried,
-              (const __nv_bfloat16*)q, ldq, H, dim, rot_dim, kv_rank, stored, positions, cos, sin, (__nv_bfloat16*)out, num_tokens);
+              (const __nv_bfloat16*)q, ldq, H, dim, rot_dim, kv_rank, stored, positions, cos, sin, (__nv_bfloat16*)out, num_tokens,
+              interleaved);
   else return ts_fail("latent_query: unknown dtype %d", dtype);
   return 0;
 }
 
 TS_EXPORT int ts_gate_heads(int dtype, const void* x, const void* gate, long long ldg, void* out, int H, int n, int num_tokens,
                             cudaStream_t stream) {
-  TS_REQUIRE(num_tokens > 0 && H > 0 && n > 0 && x && gate && out, "gate_heads: empty input");
+  TS_REQUIRE(num_tokens > 0 && H > 0 && n > 0 && x && out, "gate_heads: empty input");
   const int threads = H * n >= 1024 ? 256 : 128;
   if (dtype == TS_F32)
     TS_LAUNCH("gate_heads", gate_heads_kernel<float>, num_tokens, threads, 0, stream, (const float*)x, (const float*)gate, ldg,
@@ -571,9 +588,9 @@ TS_EXPORT int ts_gate_heads(int dtype, const void* x, const void* gate, long lon
   return 0;
 }
 
-TS_EXPORT int ts_moe_route(const float* logits, float* gates, int num_tokens, int E, int top, cudaStream_t stream) {
+TS_EXPORT int ts_moe_route(const float* logits, float* gates, int num_tokens, int E, int top, int renorm, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && E > 0 && top > 0 && top <= E && logits && gates, "moe_route: %d of %d experts", top, E);
-  TS_LAUNCH("moe_route", moe_route_kernel, (num_tokens + 3) / 4, 128, 0, stream, logits, gates, num_tokens, E, top);
+  TS_LAUNCH("moe_route", moe_route_kernel, (num_tokens + 3) / 4, 128, 0, stream, logits, gates, num_tokens, E, top, renorm);
   return 0;
 }
 
@@ -591,16 +608,17 @@ TS_EXPORT int ts_moe_route_scored(const float* logits, const float* correction, 
 }
 
 TS_EXPORT int ts_moe_gated_activate(int dtype, const void* a, const float* gates, int rows, int E, int ff, void* out,
-                                    cudaStream_t stream) {
+                                    int act, float limit, cudaStream_t stream) {
   TS_REQUIRE(rows > 0 && E > 0 && ff > 0 && a && out, "moe_gated_activate: empty input");
+  TS_REQUIRE(act >= 0 && act < ACT_COUNT && (act != ACT_BOUNDED_SWISH || limit > 0.f), "moe_gated_activate: activation %d", act);
   // a row's columns over several blocks (four elements a thread), so that a step of few rows still fills the SMs
   const long long tiles = ((long long)E * ff + 1023) / 1024;
   const dim3 grid(rows, (unsigned)(tiles < 64 ? tiles : 64));
   if (dtype == TS_F32)
-    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<float>, grid, 256, 0, stream, (const float*)a, gates, E, ff, (float*)out);
+    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<float>, grid, 256, 0, stream, (const float*)a, gates, E, ff, (float*)out, act, limit);
   else if (dtype == TS_BF16)
     TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)a, gates, E, ff,
-              (__nv_bfloat16*)out);
+              (__nv_bfloat16*)out, act, limit);
   else return ts_fail("moe_gated_activate: unknown dtype %d", dtype);
   return 0;
 }

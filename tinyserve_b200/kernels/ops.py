@@ -12,7 +12,19 @@ import torch
 
 from . import build
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+#: gated feed-forwards: act(gate) * up.  "bounded_swish" takes a bound: with g' = min(g, bound) and
+#: u' = clamp(u, -bound, bound) it is g' sigmoid(1.702 g') (u' + 1)
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "bounded_swish": 2}
+BOUNDED_ACTIVATIONS = ("bounded_swish",)
+
+
+def activation_code(activation, limit=0.0):
+    """(kernel code, bound) of a gated activation; a bounded one needs a positive bound."""
+    if activation not in ACTIVATIONS:
+        raise ValueError(f"unknown activation {activation!r}; known: {sorted(ACTIVATIONS)}")
+    if activation in BOUNDED_ACTIVATIONS and not limit > 0:
+        raise ValueError(f"activation {activation!r} needs a positive bound")
+    return ACTIVATIONS[activation], float(limit or 0.0)
 SUPPORTED_HEAD_DIMS = tuple(range(16, 513, 16))
 _DTYPE = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -207,7 +219,7 @@ _NO_SCALE = (c_void_p(0), c_int(0), c_float(0.0))
 
 def materialize(x):
     """An ordinary tensor from what a product, a norm or a block returned."""
-    return x.materialize() if isinstance(x, (SplitPartials, PendingProduct, ScaledRows, PairSum, NormedAddend)) else x
+    return x.materialize() if isinstance(x, (SplitPartials, PendingProduct, ScaledRows, PairSum, NormedAddend, ColumnScaled)) else x
 
 
 def launch_count() -> int:
@@ -564,15 +576,15 @@ def sanitize_step(ctx, vocab_size, num_positions, max_kv_len, num_state_slots):
             c_int(view.block_table.stride(0)), c_int(view.num_pages), _stream()))
 
 
-def embed_lookup(table, ids, slot_tokens=None):
-    """float32 [T, n] = table[ids]; ids int32.  An id < 0 names a state slot (-1 - slot) whose
+def embed_lookup(table, ids, slot_tokens=None, scale=1.0):
+    """float32 [T, n] = table[ids] * scale; ids int32.  An id < 0 names a state slot (-1 - slot) whose
     last sampled token is read from ``slot_tokens`` on the device."""
     _cuda(table, ids, slot_tokens)
     T, n = ids.shape[0], table.shape[1]
     out = torch.empty(T, n, dtype=torch.float32, device=table.device)
     lib = _elementwise()
     _check(lib, lib.ts_embed_lookup(c_int(_dt(table)), _ptr(table), _ptr(ids), _ptr(out), c_int(T),
-                                    c_int(n), c_int(table.shape[0]), _ptr(slot_tokens), _stream()))
+                                    c_int(n), c_int(table.shape[0]), _ptr(slot_tokens), c_float(scale), _stream()))
     return out
 
 
@@ -598,9 +610,15 @@ def _product_add_residual(pending, residual, weight, eps):
 
 def add_rmsnorm(x, residual, weight, eps, out_dtype, rows=None, scaled_ok=False):
     """residual (float32, in place) += x; returns rmsnorm(residual) * weight as ``out_dtype``.
-    ``x`` None: no add; ``x`` may be the SplitPartials or the PendingProduct of a product.  With
+    ``x`` None: no add; ``x`` may be the SplitPartials or the PendingProduct of a product, or a
+    ColumnScaled of any of these (x times one factor per column is then what is added).  With
     ``rows`` (int32) only those rows are normalised and returned, and the residual is left as it
     is.  With ``scaled_ok`` the caller takes a ScaledRows as well (it hands it to ``linear``)."""
+    x_scale = None
+    if isinstance(x, ColumnScaled):
+        x, x_scale = x.x, x.scale
+        if isinstance(x, PendingProduct):
+            x = x.partials()
     if isinstance(x, PendingProduct):
         if (scaled_ok and rows is None and out_dtype == torch.bfloat16 and x.shape == tuple(residual.shape)
                 and residual.dtype == torch.float32 and residual.is_contiguous()):
@@ -612,11 +630,13 @@ def add_rmsnorm(x, residual, weight, eps, out_dtype, rows=None, scaled_ok=False)
         if x.shape != tuple(residual.shape):
             raise TypeError("add_rmsnorm: the partial tiles do not have the residual's shape")
         parts, x = x.args(), None
-    _cuda(x, residual, weight, rows)
+    _cuda(x, residual, weight, rows, x_scale)
     if residual.dtype != torch.float32 or not residual.is_contiguous():
         raise TypeError("the residual stream is contiguous float32")
     if x is not None and (x.dtype != out_dtype or not x.is_contiguous() or x.shape != residual.shape):
         raise TypeError("add_rmsnorm: x must be contiguous, of the compute dtype and of the residual's shape")
+    if x_scale is not None and (x_scale.shape != (residual.shape[1],) or not x_scale.is_contiguous()):
+        raise TypeError("add_rmsnorm: the column factors are one contiguous row of the residual's width")
     n = residual.shape[1]
     num_out = residual.shape[0] if rows is None else rows.shape[0]
     out = torch.empty(num_out, n, dtype=out_dtype, device=residual.device)
@@ -624,7 +644,8 @@ def add_rmsnorm(x, residual, weight, eps, out_dtype, rows=None, scaled_ok=False)
     _check(lib, lib.ts_add_rmsnorm(c_int(_DTYPE[out_dtype]), _ptr(x), _ptr(residual), _ptr(weight),
                                    c_int(_vec_flag(weight, out_dtype)), c_float(eps), _ptr(out),
                                    _ptr(rows), c_int(num_out), c_int(n),
-                                   c_int(0 if rows is not None else 1), *parts, _stream()))
+                                   c_int(0 if rows is not None else 1), *parts, _ptr(x_scale),
+                                   c_int(_vec_flag(x_scale, out_dtype) if x_scale is not None else 0), _stream()))
     return out
 
 
@@ -641,16 +662,18 @@ def rmsnorm(x, weight, eps, out=None):
     return out.view(shape)
 
 
-def gated_activation(gate_up, activation="silu", block=0):
+def gated_activation(gate_up, activation="silu", block=0, limit=0.0):
     """[rows, 2 I] -> act(gate) * up, [rows, I].  ``block`` 0: the input is gate | up; else gate
-    and up columns alternate in blocks of ``block`` (see gated_linear)."""
+    and up columns alternate in blocks of ``block`` (see gated_linear).  ``limit``: the bound of a
+    bounded activation."""
+    code, limit = activation_code(activation, limit)
     gate_up = materialize(gate_up)
     _cuda(gate_up)
     rows, two_i = gate_up.shape
     out = torch.empty(rows, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
     lib = _elementwise()
     _check(lib, lib.ts_gated_activation(c_int(_dt(gate_up)), _ptr(gate_up), _ptr(out), c_int(rows),
-                                        c_int(two_i // 2), c_int(ACTIVATIONS[activation]), c_int(block), _stream()))
+                                        c_int(two_i // 2), c_int(code), c_int(block), c_float(limit), _stream()))
     return out
 
 
@@ -659,7 +682,7 @@ def gated_activation(gate_up, activation="silu", block=0):
 GATED_BLOCK = 64
 
 
-def gated_linear(x, weight, activation="silu", block=0):
+def gated_linear(x, weight, activation="silu", block=0, limit=0.0):
     """act(gate) * up of x @ weight^T, [M, N / 2].  weight [N, K] holds gate rows then up rows
     (``block`` 0) or alternates them in blocks of ``block`` rows.  With blocks of GATED_BLOCK, up
     to FUSED_MAX_TOKENS tokens and a product that needs no cut along K, the tcgen05 product does
@@ -667,6 +690,8 @@ def gated_linear(x, weight, activation="silu", block=0):
     ScaledRows that add_rmsnorm returned."""
     rows = x.data if isinstance(x, ScaledRows) else x
     N, K = weight.shape
+    if activation in BOUNDED_ACTIVATIONS:      # (the products' epilogues know the unbounded activations)
+        return gated_activation(linear(x, weight), activation, block, limit)
     if (block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
             and rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _pair_ok(rows, weight)
             and (rows.shape[0] >= PAIR_MIN_TOKENS
@@ -822,7 +847,7 @@ def decode_splits(num_requests, max_kv_len, num_heads, num_kv_heads):
 
 
 def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first=0, sinks=None, chunk=0,
-                   slopes=None):
+                   slopes=None, softcap=0.0):
     """The one-token requests of a mixed batch, by the tensor-core decode kernel."""
     T, H, D = q.shape
     Hkv = k_cache.shape[1]
@@ -840,7 +865,7 @@ def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, kee
         c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale), c_int(window),
         c_int(num_splits), _ptr(part_o), _ptr(part_ml), c_int(2 if cluster else 1), _ptr(work.dec_req),
         _ptr(work.dec_tok), c_int(n), c_int(0), c_int(_tma_pages(k_cache, v_cache)), c_int(keep_first), _ptr(sinks),
-        c_int(chunk), _ptr(slopes), _stream()),
+        c_int(chunk), _ptr(slopes), c_float(softcap), _stream()),
         2 if num_splits > 1 and not cluster else 1)
 
 
@@ -876,13 +901,14 @@ def biased_attention_backends(dtype, head_dim, page_size) -> list:
 
 
 def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None, backend=None, keep_first=0,
-                    sinks=None, chunk=0, slopes=None):
+                    sinks=None, chunk=0, slopes=None, softcap=0.0):
     """Attention of this step's queries over their requests' cached keys and values.
     ``chunk`` > 0: a query at position i sees key j <= i only if i // chunk == j // chunk (chunks
     count from position 0 of the sequence; no window beside it).  ``slopes`` float32 [H]: head h's
     score of (i, j) loses slopes[h] * (i - j) after the scale.
     ``keep_first`` (with a window): the first keys of a sequence stay visible to every later query.
     ``sinks`` float32 [H]: head h's softmax sum holds one more term exp(sinks[h]) without key or value.
+    ``softcap`` c > 0: the scaled score s becomes c tanh(s / c) (before the slopes' bias).
     q [T, H, D]; caches [pages, Hkv, page_size, D]; ``view`` a GroupView; ``ctx`` gives cu_q,
     kv_lens and the batch's maxima.  bfloat16 runs on the tensor cores (a decode kernel when
     every request brings one token, else a prefill kernel); float32 on the 32-bit kernel.
@@ -896,6 +922,9 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         raise TypeError("paged_attention: sinks are float32 [heads] on the device")
     keep_first = int(keep_first) if window > 0 else 0
     chunk = int(chunk or 0)
+    softcap = float(softcap or 0.0)
+    if softcap < 0:
+        raise ValueError("paged_attention: a soft cap is positive (0: none)")
     if chunk < 0 or (chunk and window > 0):
         raise ValueError("paged_attention: a chunk is positive and comes without a window")
     if slopes is not None and (slopes.dtype != torch.float32 or slopes.shape != (H,) or not slopes.is_cuda):
@@ -914,14 +943,15 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         tile_queries = prefill_tile_queries(q.dtype, H, Hkv, D, page)
         work = attention_work(ctx, tile_queries, q.device)
         if work.num_decode:
-            _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first, sinks, chunk, slopes)
+            _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first, sinks, chunk, slopes, softcap)
         if work.num_tiles:
             _check(lib, lib.ts_paged_attention_tcgen05(
                 _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
                 _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H), c_int(Hkv),
                 c_int(k_cache.shape[0]), c_int(page), c_int(view.block_table.stride(0)), c_float(scale),
                 c_int(window), _ptr(work.tile_req), _ptr(work.tile_q0), c_int(work.num_tiles),
-                c_int(tile_queries), c_int(keep_first), _ptr(sinks), c_int(chunk), _ptr(slopes), _stream()))
+                c_int(tile_queries), c_int(keep_first), _ptr(sinks), c_int(chunk), _ptr(slopes), c_float(softcap),
+                _stream()))
         return out
     if num_splits is None:
         if decode:
@@ -949,7 +979,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             tile_queries = rows // group if group < rows else 1
             work = attention_work(ctx, tile_queries, q.device)
             if work.num_decode:
-                _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first, sinks, chunk, slopes)
+                _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, keep_first, sinks, chunk, slopes, softcap)
             if not work.num_tiles:
                 return out
             tile_req, tile_q0, num_tiles = work.tile_req, work.tile_q0, work.num_tiles
@@ -959,7 +989,8 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale),
             c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml),
             c_int((2 if cluster else 1) if decode else 0), _ptr(tile_req), _ptr(tile_q0), c_int(num_tiles), c_int(tile_queries),
-            c_int(_tma_pages(k_cache, v_cache)), c_int(keep_first), _ptr(sinks), c_int(chunk), _ptr(slopes), _stream()),
+            c_int(_tma_pages(k_cache, v_cache)), c_int(keep_first), _ptr(sinks), c_int(chunk), _ptr(slopes),
+            c_float(softcap), _stream()),
             launches)
         return out
     lib = _attention(D)
@@ -968,7 +999,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         _ptr(ctx.cu_q), _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len),
         c_int(H), c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)),
         c_float(scale), c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), c_int(keep_first),
-        _ptr(sinks), c_int(chunk), _ptr(slopes), _stream()),
+        _ptr(sinks), c_int(chunk), _ptr(slopes), c_float(softcap), _stream()),
         launches)
     return out
 
@@ -1141,6 +1172,59 @@ class PairSum:
         return out
 
 
+class ColumnScaled:
+    """A sub-layer's output that joins the stream multiplied by one learned factor per column
+    (a layer scale): the kernel that adds it to the 32-bit residual multiplies while it loads, in
+    32-bit, so the product is never rounded to the compute dtype.  ``x`` is a tensor or an
+    unfinished product (SplitPartials, PendingProduct); ``materialize()`` gives the scaled tensor
+    to any other consumer."""
+
+    def __init__(self, x, scale):
+        if isinstance(x, (PairSum, NormedAddend, ScaledRows, ColumnScaled)):
+            x = materialize(x)
+        self.x, self.scale = x, scale
+        self.shape, self.dtype, self.device = tuple(x.shape), x.dtype, x.device
+
+    def materialize(self):
+        rows, n = self.shape
+        summed = torch.zeros(rows, n, dtype=torch.float32, device=self.device)
+        stream_add_(summed, self)
+        return summed if self.dtype == torch.float32 else summed.to(self.dtype)
+
+
+def stream_add_(residual, pending=None, first=None):
+    """residual (float32 [rows, n], in place) += pending + first.  ``pending``: None, a tensor of
+    the compute dtype, the unfinished product of one, or a ColumnScaled; ``first``: None or
+    float32 rows.  One kernel; every addend enters the sum in 32-bit."""
+    x_scale = None
+    if isinstance(pending, ColumnScaled):
+        pending, x_scale = pending.x, pending.scale
+    if isinstance(pending, PendingProduct):
+        pending = pending.partials()
+    parts = _NO_PARTIALS
+    if isinstance(pending, SplitPartials):
+        if pending.shape != tuple(residual.shape):
+            raise TypeError("stream_add: the partial tiles do not have the residual's shape")
+        parts, dtype, pending = pending.args(), pending.dtype, None
+    else:
+        pending = materialize(pending)
+        dtype = pending.dtype if pending is not None else torch.float32
+    _cuda(residual, pending, x_scale, first)
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise TypeError("the residual stream is contiguous float32")
+    for t in (pending, first):
+        if t is not None and (t.shape != residual.shape or not t.is_contiguous()):
+            raise TypeError("stream_add: addends are contiguous and of the residual's shape")
+    if first is not None and first.dtype != torch.float32:
+        raise TypeError("stream_add: the kept stream is float32")
+    rows, n = residual.shape
+    lib = _elementwise()
+    _check(lib, lib.ts_stream_add(c_int(_DTYPE[dtype]), _ptr(residual), _ptr(pending), _ptr(x_scale),
+                                  c_int(_vec_flag(x_scale, dtype) if x_scale is not None else 0), _ptr(first),
+                                  c_int(rows), c_int(n), *parts, _stream()))
+    return residual
+
+
 def _addends(x):
     if x is None:
         return None, None
@@ -1233,16 +1317,29 @@ def _columns(t):
 
 
 def rope_unit_kvwrite(q, k, v, positions, num_heads, num_kv_heads, dim, vdim, stored_dim, rotary=None,
-                      unit_norm=False, eps=0.0, k_cache=None, v_cache=None, slot_mapping=None, page_size=0):
+                      unit_norm=False, eps=0.0, k_cache=None, v_cache=None, slot_mapping=None, page_size=0,
+                      q_weight=None, k_weight=None, pre_eps=0.0, maps=1):
     """Rotary encoding of q and k (first ``rotary.rotary_dim`` elements of every head), then, with
     ``unit_norm``, division of every head of q and k by its root mean square over ``dim``; q goes
     to a [T, H, stored_dim] tensor (returned), k and v to the cache slots of ``slot_mapping``
     (None: nothing is written), heads padded with zeros to ``stored_dim``.  q [T, H dim],
-    k [T, Hkv dim], v [T, Hkv vdim] may be column ranges of one projection."""
-    _cuda(q, k, v, positions, k_cache, v_cache, slot_mapping)
+    k [T, Hkv dim], v [T, Hkv vdim] may be column ranges of one projection.
+
+    ``q_weight`` / ``k_weight`` ([dim] each): every head of q and k is RMS-normed with that weight
+    (``pre_eps``) before the rotation.  ``maps`` M > 1: every head has M score maps over the same
+    values; ``num_heads`` and ``num_kv_heads`` then count (head, map) pairs, laid out head by head
+    in q and k, v holds ``num_kv_heads`` / M heads, and the returned query rows and the cache heads
+    are arranged so that the attention kernels pair map m of a head with map m of its key/value
+    head and a copy of that head's value (``map_difference`` reads the output in that order)."""
+    _cuda(q, k, v, positions, k_cache, v_cache, slot_mapping, q_weight, k_weight)
     T = q.shape[0]
-    if q.shape[1] != num_heads * dim or k.shape[1] != num_kv_heads * dim or v.shape[1] != num_kv_heads * vdim:
+    if maps < 1 or num_heads % maps or num_kv_heads % maps:
+        raise ValueError("rope_unit_kvwrite: the maps do not divide the heads")
+    if q.shape[1] != num_heads * dim or k.shape[1] != num_kv_heads * dim or v.shape[1] != num_kv_heads // maps * vdim:
         raise ValueError("rope_unit_kvwrite: q, k, v do not have heads x size columns")
+    if (q_weight is None) != (k_weight is None) or (q_weight is not None and (
+            q_weight.dtype != k_weight.dtype or q_weight.shape != (dim,) or k_weight.shape != (dim,))):
+        raise TypeError("rope_unit_kvwrite: q and k norm weights come together, [dim] each and alike in dtype")
     if k_cache is not None and (k_cache.dtype != q.dtype or k_cache.shape[-1] != stored_dim or not k_cache.is_contiguous()
                                 or not v_cache.is_contiguous()):
         raise TypeError("rope_unit_kvwrite: the cache does not fit the activations")
@@ -1254,7 +1351,24 @@ def rope_unit_kvwrite(q, k, v, positions, num_heads, num_kv_heads, dim, vdim, st
         c_int(_dt(q)), *_columns(q), *_columns(k), *_columns(v), _ptr(out), _ptr(positions), _ptr(cos), _ptr(sin),
         c_int(rotary.rotary_dim if rotary is not None else 0), c_int(int(rotary.interleaved) if rotary is not None else 0),
         c_int(1 if unit_norm else 0), c_float(eps), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(dim),
-        c_int(vdim), c_int(stored_dim), _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), c_int(page_size), _stream()))
+        c_int(vdim), c_int(stored_dim), _ptr(k_cache), _ptr(v_cache), _ptr(slot_mapping), c_int(page_size),
+        _ptr(q_weight), _ptr(k_weight), c_int(_vec_flag(q_weight, q.dtype) if q_weight is not None else 0),
+        c_float(pre_eps), c_int(maps), _stream()))
+    return out
+
+
+def map_difference(attn, num_heads, num_kv_heads, vdim, factor, eps, post):
+    """[T, H * vdim] from attn [T, 2 H, D], the outputs of two score maps per head in the row order
+    of ``rope_unit_kvwrite(maps=2)``: d = a_0 - factor * a_1 over the first ``vdim`` columns of a
+    head, then d / sqrt(mean(d^2) + eps) * post, in 32-bit."""
+    _cuda(attn)
+    T, rows, D = attn.shape
+    if rows != 2 * num_heads or not attn.is_contiguous() or num_heads % num_kv_heads or vdim > D:
+        raise ValueError("map_difference: attn is contiguous [T, 2 heads, D]")
+    out = torch.empty(T, num_heads * vdim, dtype=attn.dtype, device=attn.device)
+    lib = _elementwise()
+    _check(lib, lib.ts_map_difference(c_int(_dt(attn)), _ptr(attn), _ptr(out), c_int(T), c_int(num_heads), c_int(num_kv_heads),
+                                      c_int(D), c_int(vdim), c_float(factor), c_float(eps), c_float(post), _stream()))
     return out
 
 
@@ -1460,7 +1574,7 @@ def latent_prepare(proj, q_rank, q_weight, eps, kv_rank=0, rot_dim=0, kv_weight=
         c_int(stored), c_int(1 if has_kv else 0), _ptr(q_weight), c_int(_vec_flag(q_weight, proj.dtype)), _ptr(kv_weight),
         c_int(_vec_flag(kv_weight, proj.dtype) if has_kv else 0), c_float(eps), _ptr(positions),
         _ptr(rotary.cos if rotary is not None else None), _ptr(rotary.sin if rotary is not None else None), _ptr(q_latent),
-        _ptr(cache), _ptr(slot_mapping), c_int(T), _stream()))
+        _ptr(cache), _ptr(slot_mapping), c_int(T), c_int(int(rotary.interleaved) if rotary is not None else 0), _stream()))
     return q_latent
 
 
@@ -1478,20 +1592,22 @@ def latent_query(carried, q, num_heads, dim, rot_dim, stored, rotary, positions)
     _check(lib, lib.ts_latent_query(
         c_int(_dt(q)), _ptr(carried), _ptr(q), c_longlong(q.stride(0)), c_int(H), c_int(dim), c_int(rot_dim), c_int(kv_rank),
         c_int(stored), _ptr(positions), _ptr(rotary.cos if rotary is not None else None),
-        _ptr(rotary.sin if rotary is not None else None), _ptr(out), c_int(T), _stream()))
+        _ptr(rotary.sin if rotary is not None else None), _ptr(out), c_int(T),
+        c_int(int(rotary.interleaved) if rotary is not None else 0), _stream()))
     return out
 
 
-def gate_heads(x, gate):
-    """[T, H * n] = x [H, T, n] * sigmoid(gate [T, H * n]); ``gate`` may be a column range."""
+def gate_heads(x, gate=None):
+    """[T, H * n] = x [H, T, n] * sigmoid(gate [T, H * n]); ``gate`` may be a column range, or None:
+    the heads are laid side by side as they are."""
     _cuda(x, gate)
     H, T, n = x.shape
-    if not x.is_contiguous() or gate.shape != (T, H * n) or gate.stride(1) != 1 or gate.dtype != x.dtype:
+    if not x.is_contiguous() or (gate is not None and (gate.shape != (T, H * n) or gate.stride(1) != 1 or gate.dtype != x.dtype)):
         raise ValueError("gate_heads: operands do not fit")
     out = torch.empty(T, H * n, dtype=x.dtype, device=x.device)
     lib = _latent_moe()
-    _check(lib, lib.ts_gate_heads(c_int(_dt(x)), _ptr(x), _ptr(gate), c_longlong(gate.stride(0)), _ptr(out), c_int(H), c_int(n),
-                                  c_int(T), _stream()))
+    _check(lib, lib.ts_gate_heads(c_int(_dt(x)), _ptr(x), _ptr(gate), c_longlong(gate.stride(0) if gate is not None else 0),
+                                  _ptr(out), c_int(H), c_int(n), c_int(T), _stream()))
     return out
 
 
@@ -1516,16 +1632,18 @@ def batched_matmul(a, b):
 
 
 # ----------------------------------------------------------------------------- mixture of experts
-def moe_route(logits, top):
+def moe_route(logits, top, renormalize=False):
     """float32 [T, E] router logits -> float32 [T, E]: softmax over all experts, the ``top`` largest
-    keep their probability as it is, the others become zero."""
+    keep their probability as it is, the others become zero.  With ``renormalize`` the kept ones are
+    divided by their sum: the softmax over the chosen logits alone."""
     _cuda(logits)
     if logits.dtype != torch.float32 or not logits.is_contiguous():
         raise TypeError("moe_route: router logits are contiguous float32")
     T, E = logits.shape
     gates = torch.empty_like(logits)
     lib = _latent_moe()
-    _check(lib, lib.ts_moe_route(_ptr(logits), _ptr(gates), c_int(T), c_int(E), c_int(top), _stream()))
+    _check(lib, lib.ts_moe_route(_ptr(logits), _ptr(gates), c_int(T), c_int(E), c_int(top), c_int(1 if renormalize else 0),
+                                 _stream()))
     return gates
 
 
@@ -1552,7 +1670,7 @@ def moe_activate_(a, gates, num_experts, logits=None, top=0):
 MOE_GROUPED_MIN_TOKENS = 256
 
 
-def moe_grouped(h, gates, up, down_side_by_side, top, gated=False):
+def moe_grouped(h, gates, up, down_side_by_side, top, gated=False, activation="silu", limit=0.0):
     """Mixture of experts over rows sorted by expert.  h [T, n] bfloat16; gates float32 [T, E] (zero:
     not chosen); up [E ff, n] (expert by expert); down_side_by_side [n, E ff].  Returns [T, n]:
     sum over a token's experts of gate * W_down,e relu(W_up,e h)^2, the sum in 32-bit.  The two
@@ -1571,7 +1689,8 @@ def moe_grouped(h, gates, up, down_side_by_side, top, gated=False):
     x = torch.empty(capacity, n, dtype=h.dtype, device=h.device)
     _check(lib, lib.ts_moe_gather(c_int(_dt(h)), _ptr(h), _ptr(row_token), _ptr(x), c_int(capacity), c_int(n), _stream()))
     if gated:
-        a = moe_gated_activate(torch.nn.functional.grouped_mm(x, up.view(E, 2 * ff, n).transpose(1, 2), offs=ends), None, 1)
+        a = moe_gated_activate(torch.nn.functional.grouped_mm(x, up.view(E, 2 * ff, n).transpose(1, 2), offs=ends), None, 1,
+                               activation, limit)
     else:
         a = torch.nn.functional.grouped_mm(x, up.view(E, ff, n).transpose(1, 2), offs=ends)
         _check(lib, lib.ts_moe_activate(c_int(_dt(a)), _ptr(a), None, c_int(capacity), c_int(1), c_int(ff), None, c_int(0), _stream()))
@@ -1790,10 +1909,12 @@ def moe_route_scored(logits, correction, top, groups=1, keep=1):
     return gates
 
 
-def moe_gated_activate(a, gates, num_experts):
+def moe_gated_activate(a, gates, num_experts, activation="silu", limit=0.0):
     """a [rows, E * 2 ff] (per expert: gate rows, then up rows) -> [rows, E * ff] =
-    silu(gate) * up * gates[row, e]; ``gates`` None: no weight (rows that are sorted by expert)."""
+    act(gate) * up * gates[row, e] (``activation`` as in ``gated_activation``); ``gates`` None: no
+    weight (rows that are sorted by expert)."""
     _cuda(a, gates)
+    code, limit = activation_code(activation, limit)
     rows = a.shape[0]
     ff = a.shape[1] // (2 * num_experts)
     if not a.is_contiguous() or a.shape[1] != 2 * ff * num_experts or \
@@ -1802,5 +1923,5 @@ def moe_gated_activate(a, gates, num_experts):
     out = torch.empty(rows, num_experts * ff, dtype=a.dtype, device=a.device)
     lib = _latent_moe()
     _check(lib, lib.ts_moe_gated_activate(c_int(_dt(a)), _ptr(a), _ptr(gates), c_int(rows), c_int(num_experts), c_int(ff),
-                                          _ptr(out), _stream()))
+                                          _ptr(out), c_int(code), c_float(limit), _stream()))
     return out

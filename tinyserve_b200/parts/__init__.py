@@ -11,6 +11,6 @@ from .linear_attention import HGRN2, MLSTM, GatedLinearAttention, Lightning, Mam
 from .latent_attention import LatentAttention
 from .moe import MixtureOfExperts
 from .side_by_side import SideBySide
-from .stream import InputInjection
+from .stream import InputAdd, InputInjection
 from .block import ARRANGEMENTS, ParallelBlock, PostNormBlock, PreNormBlock, SandwichBlock, build_block
 from .model import BoundCall, DecoderModel, Embedding, LMHead, build_model

@@ -25,7 +25,18 @@ all their heads at once, before they are split into heads, with one weight per c
 position 0 of the sequence); ``distance_slopes`` (one slope per head: slope * (i - j) is taken off
 the scaled score); ``sinks`` (a learned number per head whose exponential joins the softmax sum,
 without key or value); ``out_gate`` (the concatenated heads times sigmoid(W_g h), element by
-element, before the output projection).  Biases on q, k and v go with all of them."""
+element, before the output projection).  Biases on q, k and v go with all of them.
+
+``softcap`` c > 0: the scaled score s becomes c tanh(s / c) before the softmax.
+
+``differential`` = {"diff": d, "eps": e}: every head has two score maps over the same values.  q
+holds 2 dim columns per head and k 2 dim per key/value head, [map 1 | map 2]; each map is normed
+(``qk_norm``), rotated, capped and softmaxed on its own and gives an output a_1, a_2 over the
+head's values; with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + d (four learned vectors of dim
+elements, one number per layer, made once in 32-bit) the head's output is
+o = a_1 - lambda a_2, divided by sqrt(mean(o^2) + e) over its value columns and multiplied by 1 - d.
+The attention kernels run it as 2 H query heads on 2 G key/value heads (the value of a key/value
+head is kept beside both of its maps' keys); ``ops.map_difference`` then combines the pairs."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -34,7 +45,8 @@ from .base import (CacheSpec, Mixer, ParamSpec, Source, build_norm, build_positi
 
 
 DEFAULT_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm",
-                 "gate": "g_proj", "sinks": "sinks"}
+                 "gate": "g_proj", "sinks": "sinks", "lambda_q1": "lq1", "lambda_k1": "lk1", "lambda_q2": "lq2",
+                 "lambda_k2": "lk2"}
 
 
 class Attention(Mixer):
@@ -44,7 +56,7 @@ class Attention(Mixer):
     def __init__(self, hidden_size, num_heads, num_kv_heads, head_dim, bias=False, qk_norm=None,
                  position=None, window=0, scale=None, names=None, value_dim=None, unit_norm_eps=None,
                  head_gate=False, keep_first=0, joint_norm=False, norm_eps=0.0, chunk=0, distance_slopes=None,
-                 sinks=False, out_gate=False):
+                 sinks=False, out_gate=False, softcap=0.0, differential=None):
         super().__init__()
         self.names = dict(DEFAULT_NAMES, **(names or {}))
         if num_heads % num_kv_heads:
@@ -73,19 +85,29 @@ class Attention(Mixer):
         if self.out_gate and self.head_gate:
             raise ValueError("attention: one gate, per head or per element")
         extended = self.joint_norm or self.chunk > 0 or self.slope_values is not None or self.has_sinks or self.out_gate
+        self.softcap = float(softcap or 0.0)
+        if self.softcap < 0:
+            raise ValueError("attention: a soft cap is positive (0: none)")
+        self.differential = dict(differential) if differential else None
+        self.maps = 2 if self.differential else 1
+        if self.differential and (extended or self.head_gate or self.unit_norm_eps is not None or bias):
+            raise ValueError("attention: two score maps come with a per-head q/k norm, rotation, a window and a soft cap only")
         self.general = (self.value_dim != head_dim or self.unit_norm_eps is not None or self.head_gate
-                        or self.keep_first > 0 or extended)
-        if self.general and (qk_norm is not None or (bias and not extended)):
-            raise ValueError("attention: a value size of its own, the unit norm and the head gate come "
-                             "without a weighted q/k norm and without biases")
+                        or self.keep_first > 0 or extended or self.softcap > 0 or self.maps > 1)
+        if self.general and ((qk_norm is not None and (extended or self.unit_norm_eps is not None))
+                             or (bias and not extended)):
+            raise ValueError("attention: the unit norm and the forms with a joint norm, chunks, slopes, sinks or an output "
+                             "gate come without a weighted per-head q/k norm; a value size of its own, the unit norm and "
+                             "the head gate come without biases")
         if self.joint_norm and (self.unit_norm_eps is not None or position is not None):
             raise ValueError("attention: the norm over all heads comes without rotation and without the unit norm")
         self.slopes = self.sinks = None
         widest = max(head_dim, self.value_dim)
         self.stored_dim = -(-widest // 16) * 16 if self.general else head_dim
-        self.q_size = num_heads * head_dim
-        self.kv_size = num_kv_heads * head_dim
+        self.q_size = num_heads * self.maps * head_dim
+        self.kv_size = num_kv_heads * self.maps * head_dim
         self.v_size = num_kv_heads * self.value_dim
+        self.map_factor = None       # lambda of the two maps, made when the tensors are bound
         self.gate_size = num_heads if self.head_gate else (num_heads * self.value_dim if self.out_gate else 0)
 
     def children(self):
@@ -120,6 +142,10 @@ class Attention(Mixer):
                                                sources=(Source(f"{nm['k_norm']}.weight", 0, kv),))
         if self.has_sinks:
             specs["sinks"] = ParamSpec((self.num_heads,), role="vector", init="wide", sources=(Source(nm["sinks"], 0, self.num_heads),))
+        if self.differential:
+            for key in ("lambda_q1", "lambda_k1", "lambda_q2", "lambda_k2"):
+                # (drawn wide in the random-weights mode, so that lambda is far from the constant it starts from)
+                specs[key] = ParamSpec((self.head_dim,), role="vector", init="normal", sources=(Source(nm[key], 0, self.head_dim),))
         return specs
 
     def bind(self, tensors):
@@ -128,6 +154,11 @@ class Attention(Mixer):
             tensors["qkv_proj.bias"][self.q_size + self.kv_size + self.v_size:] = 0
         if "sinks" in tensors:
             tensors["sinks"] = tensors["sinks"].float().contiguous()       # they join a 32-bit sum
+        if self.differential and "lambda_q1" in tensors:
+            import math
+            dot = lambda a, b: float((tensors[a].float() * tensors[b].float()).sum())
+            self.map_factor = (math.exp(dot("lambda_q1", "lambda_k1")) - math.exp(dot("lambda_q2", "lambda_k2"))
+                               + float(self.differential["diff"]))
         super().bind(tensors)
 
     def prepare(self, runtime):
@@ -138,7 +169,7 @@ class Attention(Mixer):
 
     def cache_spec(self):
         kind = "window" if self.window > 0 else "full"
-        return CacheSpec(kind, self.num_kv_heads, self.stored_dim, self.window, keep_first=self.keep_first)
+        return CacheSpec(kind, self.num_kv_heads * self.maps, self.stored_dim, self.window, keep_first=self.keep_first)
 
     def _biased(self):
         return self.chunk > 0 or self.slope_values is not None
@@ -146,7 +177,8 @@ class Attention(Mixer):
     accepts_scaled_rows = True
 
     def work_tile_queries(self, dtype, page_size):
-        return ops.prefill_tile_queries(dtype, self.num_heads, self.num_kv_heads, self.stored_dim, page_size)
+        return ops.prefill_tile_queries(dtype, self.num_heads * self.maps, self.num_kv_heads * self.maps, self.stored_dim,
+                                        page_size)
 
     def _forward_general(self, h, ctx, call):
         qkv = ops.materialize(ops.linear(h, self.w["qkv_proj.weight"], self.w.get("qkv_proj.bias")))
@@ -169,13 +201,22 @@ class Attention(Mixer):
             else:
                 out = out.view(out.shape[0], self.num_heads * self.value_dim)
             return ops.linear(out, self.w["o_proj.weight"], allow_pending=True)
+        M = self.maps
         q = ops.rope_unit_kvwrite(
-            qkv[:, :q_end], qkv[:, q_end:k_end], qkv[:, k_end:v_end], ctx.positions, self.num_heads,
-            self.num_kv_heads, self.head_dim, self.value_dim, self.stored_dim, rotary=self.position,
+            qkv[:, :q_end], qkv[:, q_end:k_end], qkv[:, k_end:v_end], ctx.positions, self.num_heads * M,
+            self.num_kv_heads * M, self.head_dim, self.value_dim, self.stored_dim, rotary=self.position,
             unit_norm=self.unit_norm_eps is not None, eps=self.unit_norm_eps or 0.0, k_cache=cache.k, v_cache=cache.v,
-            slot_mapping=view.slot_mapping if call.writes_cache else None, page_size=view.page_size)
-        out = ops.paged_attention(q, cache.k, cache.v, view, ctx, self.scale, self.window, keep_first=self.keep_first)
-        if self.head_gate or self.stored_dim != self.value_dim:
+            slot_mapping=view.slot_mapping if call.writes_cache else None, page_size=view.page_size,
+            q_weight=self.q_norm.w["weight"] if self.q_norm is not None else None,
+            k_weight=self.k_norm.w["weight"] if self.k_norm is not None else None,
+            pre_eps=self.q_norm.eps if self.q_norm is not None else 0.0, maps=M)
+        out = ops.paged_attention(q, cache.k, cache.v, view, ctx, self.scale, self.window, keep_first=self.keep_first,
+                                  softcap=self.softcap)
+        if M > 1:
+            d = self.differential
+            out = ops.map_difference(out, self.num_heads, self.num_kv_heads, self.value_dim, self.map_factor,
+                                     float(d["eps"]), 1.0 - float(d["diff"]))
+        elif self.head_gate or self.stored_dim != self.value_dim:
             out = ops.head_gate(out, qkv[:, v_end:] if self.head_gate else None, self.value_dim)
         else:
             out = out.view(out.shape[0], self.num_heads * self.value_dim)

@@ -44,25 +44,47 @@ def residual_compute_dtype(norm, x):
 
 
 class PreNormBlock(Part):
+    """r <- r + mixer(norm1(r)), then r <- r + ffn(norm2(r)).  A layer without a feed-forward
+    (``LayerSpec.ffn`` None) has the first line only.  With ``LayerSpec.options["layer_scale"]``
+    each sub-layer's output is multiplied, column by column, by a learned vector before it joins the
+    stream (r <- r + s1 * mixer(..), r <- r + s2 * ffn(..)); the product is made in 32-bit by the
+    kernel that adds it to the residual (``ops.ColumnScaled``)."""
     capturable = True
 
     def __init__(self, spec: LayerSpec, hidden_size: int):
         super().__init__()
+        self.hidden_size = hidden_size
         self.mixer = build_mixer(spec.mixer)
-        self.ffn = build_feed_forward(spec.ffn)
+        self.ffn = build_feed_forward(spec.ffn) if spec.ffn is not None else None
         self.input_norm = build_norm(spec.norm, hidden_size)
-        self.post_mixer_norm = build_norm(spec.norm, hidden_size)
+        self.post_mixer_norm = build_norm(spec.norm, hidden_size) if self.ffn is not None else None
+        self.layer_scale = bool(spec.options.get("layer_scale", False))
         self._names = {
             "mixer": spec.name_of("mixer", self.mixer.tree_name),
-            "ffn": spec.name_of("ffn", self.ffn.tree_name),
+            "ffn": spec.name_of("ffn", self.ffn.tree_name if self.ffn is not None else ""),
             "input_norm": spec.name_of("input_norm"),
             "post_mixer_norm": spec.name_of("post_mixer_norm"),
+            "mixer_scale": spec.name_of("mixer_scale", "mixer_scale"),
+            "ffn_scale": spec.name_of("ffn_scale", "ffn_scale"),
         }
 
     def children(self):
         n = self._names
-        return {n["mixer"]: self.mixer, n["ffn"]: self.ffn, n["input_norm"]: self.input_norm,
-                n["post_mixer_norm"]: self.post_mixer_norm}
+        out = {n["mixer"]: self.mixer, n["input_norm"]: self.input_norm}
+        if self.ffn is not None:
+            out.update({n["ffn"]: self.ffn, n["post_mixer_norm"]: self.post_mixer_norm})
+        return out
+
+    def param_specs(self):
+        if not self.layer_scale:
+            return {}
+        specs = {self._names["mixer_scale"]: ParamSpec((self.hidden_size,), role="vector", init="norm_weight")}
+        if self.ffn is not None:
+            specs[self._names["ffn_scale"]] = ParamSpec((self.hidden_size,), role="vector", init="norm_weight")
+        return specs
+
+    def _scaled(self, x, which):
+        return ops.ColumnScaled(x, self.w[self._names[which]]) if self.layer_scale else x
 
     def forward(self, x, residual, ctx, call):
         """(x, residual) -> x of the next block; ``residual`` (32-bit) is updated in place.
@@ -70,11 +92,13 @@ class PreNormBlock(Part):
         h = add_and_norm(self.input_norm, x, residual, self.mixer, compute_dtype=ctx.dtype)
         if not getattr(self.mixer, "accepts_scaled_rows", False):
             h = ops.materialize(h)
-        x = self.mixer.forward(h, ctx, call)
+        x = self._scaled(self.mixer.forward(h, ctx, call), "mixer_scale")
+        if self.ffn is None:
+            return x
         h = add_and_norm(self.post_mixer_norm, x, residual, self.ffn, compute_dtype=ctx.dtype)
         if not getattr(self.ffn, "accepts_scaled_rows", False):
             h = ops.materialize(h)
-        return self.ffn.forward(h, ctx)
+        return self._scaled(self.ffn.forward(h, ctx), "ffn_scale")
 
 
 class ParallelBlock(Part):

@@ -10,8 +10,10 @@ query [q_a | q'_a] (``dim`` plain and ``rot_dim`` rotated columns of W_uq rmsnor
 so the attention kernel sees one key/value head whose rows are [c_j | r_j] (the cache rows as they
 are, keys and values alike), H query heads of ``kv_rank + rot_dim`` columns, and returns per head
 the weighted sum of the latents, which W_uv,a then expands.  The softmax sum of head a holds one
-more term exp(sink_a) (a learned number per head, no key, no value, not scaled); the concatenated
-heads are multiplied by sigmoid(W_g h) before the output projection.
+more term exp(sink_a) (a learned number per head, no key, no value, not scaled; ``sink`` False:
+the ordinary softmax); the concatenated heads are multiplied by sigmoid(W_g h) before the output
+projection (``gate`` False: they are not).  The rotated parts of q and k turn as the position
+encoding says: pairs (i, i + rot_dim/2) or neighbours (2i, 2i + 1), frequencies stretched or not.
 
 A layer built with ``own_kv`` False has no W_dkv: it reads the cache entry that another layer of
 the same geometry writes (``LayerCall.cache`` / ``writes_cache``) with its own W_uk, W_uv and
@@ -30,17 +32,17 @@ class LatentAttention(Mixer):
     capturable = True
 
     def __init__(self, hidden_size, num_heads, head_dim, rot_dim, value_dim, q_rank, kv_rank, scale, eps,
-                 position=None, own_kv=True, sink=True, names=None):
+                 position=None, own_kv=True, sink=True, names=None, gate=True):
         super().__init__()
         self.names = dict(DEFAULT_NAMES, **(names or {}))
         self.hidden_size, self.num_heads = hidden_size, num_heads
         self.head_dim, self.rot_dim, self.value_dim = head_dim, int(rot_dim), value_dim
         self.q_rank, self.kv_rank = q_rank, kv_rank
         self.scale, self.eps = float(scale), float(eps)
-        self.own_kv, self.sink = bool(own_kv), bool(sink)
+        self.own_kv, self.sink, self.gate = bool(own_kv), bool(sink), bool(gate)
         self.position = build_position_encoding(position) if position is not None and self.rot_dim else None
-        if self.position is not None and (self.position.rotary_dim != self.rot_dim or self.position.interleaved):
-            raise ValueError("latent attention: the rotated part is rotated as a whole, in the (i, i + n/2) pairing")
+        if self.position is not None and self.position.rotary_dim != self.rot_dim:
+            raise ValueError("latent attention: the rotated part is rotated as a whole")
         if self.rot_dim % 2:
             raise ValueError("latent attention: the rotated part has an even size")
         #: width of a cache row and of a query row: what the attention kernels take
@@ -60,7 +62,7 @@ class LatentAttention(Mixer):
         nm, H = self.names, self.num_heads
         # the three products that read the mixer's input are one: query latent | kv latent + shared key part | gate
         rows, at = [], 0
-        for name, n in ((nm["q_down"], self.q_rank), (nm["kv_down"], self.kv_size), (nm["gate"], self.v_size)):
+        for name, n in ((nm["q_down"], self.q_rank), (nm["kv_down"], self.kv_size), (nm["gate"], self.v_size if self.gate else 0)):
             if n:
                 rows.append(Source(f"{name}.weight", at, at + n))
                 at += n
@@ -115,7 +117,7 @@ class LatentAttention(Mixer):
         mixed = ops.paged_attention(q_rows, rows, rows, view, ctx, self.scale, sinks=self._sinks)
         # [H, T, kv_rank] x [H, kv_rank, vdim]: every head's weighted latent expanded to its values
         values = ops.batched_matmul(mixed[:, :, :r].transpose(0, 1), self.w["v_up.weight"].view(H, nv, r).transpose(1, 2))
-        gate = proj[:, self.q_rank + self.kv_size:]
+        gate = proj[:, self.q_rank + self.kv_size:] if self.gate else None
         return ops.linear(ops.gate_heads(values, gate), self.w["o_proj.weight"], allow_pending=True)
 
 

@@ -2,7 +2,10 @@
 as one fused projection (serve.py:911-912, 916).  Its rows alternate in blocks of 64, gate rows
 then the matching up rows (when the width allows), so that a 128-row tile of the tcgen05 product
 holds both and can apply the activation in its epilogue; the activation kernel reads the same
-layout where the product is someone else's."""
+layout where the product is someone else's.
+
+``activation`` "bounded_swish" with ``limit`` L: g = min(gate(x), L), u = clamp(up(x), -L, L),
+down(g sigmoid(1.702 g) (u + 1))."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -16,11 +19,10 @@ class GatedMLP(FeedForward):
     tree_name = "mlp"
     capturable = True
 
-    def __init__(self, hidden_size, intermediate_size, activation="silu", names=None):
+    def __init__(self, hidden_size, intermediate_size, activation="silu", names=None, limit=0.0):
         super().__init__()
         self.names = dict(DEFAULT_NAMES, **(names or {}))
-        if activation not in ops.ACTIVATIONS:
-            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ops.ACTIVATIONS)}")
+        self.limit = ops.activation_code(activation, limit)[1]
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.activation = activation
         self.block = ops.GATED_BLOCK if intermediate_size % ops.GATED_BLOCK == 0 else 0
@@ -38,7 +40,7 @@ class GatedMLP(FeedForward):
     accepts_scaled_rows = True
 
     def forward(self, h, ctx):
-        act = ops.gated_linear(h, self.w["gate_up_proj.weight"], self.activation, self.block)
+        act = ops.gated_linear(h, self.w["gate_up_proj.weight"], self.activation, self.block, self.limit)
         return ops.linear(act, self.w["down_proj.weight"], allow_pending=True)
 
 

@@ -170,7 +170,8 @@ class DecoderModel(Part):
     # ------------------------------------------------------------------ forward
     def forward(self, ctx):
         """Run this step's tokens; returns 32-bit logits [len(ctx.logit_rows), vocab]."""
-        residual = ops.embed_lookup(self.embed_tokens.w["weight"], ctx.token_ids, ctx.slot_tokens)
+        residual = ops.embed_lookup(self.embed_tokens.w["weight"], ctx.token_ids, ctx.slot_tokens,
+                                    scale=self.spec.embedding_scale)
         if self.embed_position is not None:
             self.embed_position.add_to_embeddings(residual, ctx)
         first = residual.clone() if any(op.needs_first for op in self.stream_ops.values()) else None

@@ -3,7 +3,10 @@
 ``InputInjection``: before pass t of a group of layers that runs several times with the same
 weights, the stream is mixed with the embedding output again, r <- W [r; r0] + step[t]
 (W [hidden, 2 hidden], the stream's columns first; step [times, hidden]).  The product takes
-[r; r0] in the compute dtype and leaves the new stream in 32-bit."""
+[r; r0] in the compute dtype and leaves the new stream in 32-bit.
+
+``InputAdd``: the plain form of the same idea, r <- r + r0: the embedding output is added to the
+stream, in 32-bit, together with whatever the block before left pending."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -32,3 +35,18 @@ class InputInjection(StreamOp):
 
 
 register_stream_op("input_injection", InputInjection)
+
+
+class InputAdd(StreamOp):
+    capturable = True
+    needs_first = True
+
+    def __init__(self, hidden_size):
+        super().__init__()
+        self.hidden_size = hidden_size
+
+    def forward(self, residual, pending, first, ctx, arg):
+        return ops.stream_add_(residual, pending, first), None
+
+
+register_stream_op("input_add", InputAdd)
