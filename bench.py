@@ -24,6 +24,11 @@ batch 8, and the design's own kernels beside the like kernels of Qwen3, each aga
 
 does the same for Delilorn (latent attention, lightning attention, attention over a window beside
 kept first tokens, a mixture of experts whose active weights equal Qwen3's feed-forward).
+
+    python bench.py --arch babadra [--sizes 2048,4096]
+
+measures Babadra (latent attention, attention with two capped score maps per head, bounded gated
+feed-forwards, dense and as experts, a repeated group of layers) beside Delilorn, the closest design.
 """
 from __future__ import annotations
 
@@ -407,6 +412,29 @@ def tarivik_shapes(width):
     return tarivik, delilorn
 
 
+def babadra_shapes(width):
+    """A Babadra of real layer sizes at ``width``: latent attention with a dense feed-forward, attention
+    with two score maps per head and experts, twice; the two middle layers run twice, which makes six
+    block runs.  The attention kernels see as many query heads of 128 on as many key/value heads as the
+    Delilorn beside it has (half as many heads, two maps each); 8 gated experts of which a token takes
+    2, sized so that a token's active expert weights equal the dense feed-forward's."""
+    delilorn, _ = delilorn_shapes(width)
+    heads, ff, vocab = width // 128, width * 11 // 4, 32768
+    rank, rot = (96, 32) if width < 4096 else (192, 64)          # cache rows of 128 and of 256
+    latent = {"heads": heads, "dim": 128, "rot_dim": rot, "vdim": 128, "q_rank": width // 2, "kv_rank": rank,
+              "scale": (128 + rot) ** -0.5,
+              "rot": {"base": 5e5, "dims": rot, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    two_maps = {"heads": heads // 2, "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "diff": 0.5,
+                "softcap": 50.0, "rot": {"base": 2.5e5, "dims": 64}}
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": (ff // 2 + 63) // 64 * 64, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
+    order = [{"type": "latent_attention", "mixer": latent, "mlp": dense}, {"type": "attention", "mixer": two_maps, "mlp": moe}]
+    babadra = {"architecture": "Babadra", "vocab": vocab, "width": width, "max_positions": CONTEXT, "norm": {"eps": 1e-6},
+               "embedding": {"scale": float(width) ** 0.5}, "logit_softcap": 30.0, "loop": {"start": 1, "stop": 3, "times": 2},
+               "layers": order + order}
+    return babadra, delilorn
+
+
 def _time_us(fn, iters=20):
     import torch
     for _ in range(3):
@@ -754,14 +782,157 @@ def tarivik_kernel_table(width, peaks):
     return out
 
 
+def babadra_kernel_table(width, peaks):
+    """Babadra's kernels beside the like kernels of Delilorn at this width, time over roofline time.  Attention
+    over one latent head (both designs: the same kernel, here without a sink); attention with two capped score
+    maps per head (the attention kernel on twice the heads with the cap, then the maps' difference) beside
+    Delilorn's window attention and plain attention of as many heads (prefill: FLOPs of the visible keys over the
+    library's GEMM rate; decode: bytes of the cached keys and values, the values once per key/value head, as
+    the design needs them); the experts with the bounded gate beside Delilorn's (prefill: FLOPs of the chosen
+    experts; decode: bytes of all experts' weights); the dense bounded feed-forward beside the gated one of
+    Qwen3; the add of a sub-layer's output times its factors with the next norm beside Delilorn's norm + add +
+    norm.  Decode launches are replayed from a graph, as the engine replays a decode step."""
+    import torch
+    from tinyserve_b200.engine.batch import GroupView, StepContext
+    from tinyserve_b200.kernels import ops
+    from tinyserve_b200.parts.moe import MixtureOfExperts
+    dev, bf = "cuda:0", torch.bfloat16
+    raw, beside = babadra_shapes(width)
+    lat, two = raw["layers"][0]["mixer"], raw["layers"][1]["mixer"]
+    dense, moe, moe_d = raw["layers"][0]["mlp"], raw["layers"][1]["mlp"], beside["layers"][0]["mlp"]
+    win = beside["layers"][3]["mixer"]
+    out = {}
+
+    def frac(key, us, roof):
+        out[key] = {"us": round(us, 1), "roofline_us": round(roof, 2), "frac": round(roof / us, 3)}
+
+    for name, lengths, starts in (("prefill_2048", [2048], [0]), ("decode_b8", [1] * 8, [2048] * 8)):
+        T, B = sum(lengths), len(lengths)
+        timed = _time_us if T > B else _time_graph_us
+        kv_len, page = starts[0] + lengths[0], 64
+        pages_per = -(-kv_len // page)
+        cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32, device=dev)
+        table = (torch.arange(B * pages_per, dtype=torch.int32, device=dev) + 1).view(B, pages_per)
+
+        def context():
+            sc = StepContext()
+            sc.num_tokens, sc.num_requests, sc.max_q_len, sc.max_kv_len = T, B, max(lengths), kv_len
+            sc.cu_q, sc.kv_lens = cu, torch.full((B,), kv_len, dtype=torch.int32, device=dev)
+            sc.host = {"cu_q": cu.tolist(), "kv_lens": [kv_len] * B}
+            return sc
+
+        def attention(H, G, D, window=0, keep=0, sinks=None, shared=False, softcap=0.0, after=None):
+            kc = torch.randn(B * pages_per + 1, G, page, D, device=dev).to(bf)
+            vc = kc if shared else torch.randn_like(kc)
+            view = GroupView(page, pages_per, None, table, kc.shape[0])
+            q = torch.randn(T, H, D, device=dev).to(bf)
+            sc = context()
+            ops.paged_attention(q, kc, vc, view, sc, D ** -0.5, window, keep_first=keep, sinks=sinks, softcap=softcap)   # (work lists)
+            run = lambda: ops.paged_attention(q, kc, vc, view, sc, D ** -0.5, window, keep_first=keep, sinks=sinks, softcap=softcap)
+            return timed((lambda: after(run())) if after else run)
+
+        def seen(window=0, keep=0):
+            pos = torch.arange(kv_len - lengths[0], kv_len)
+            n = pos + 1 if not window else torch.minimum(pos + 1, torch.full_like(pos, window)) + torch.clamp(
+                torch.minimum(pos + 1 - window, torch.full_like(pos, keep)), min=0)
+            return float(n.sum())
+
+        def attention_roof(H, D, key_heads, value_heads, window=0, keep=0):
+            if T > B:
+                return 4.0 * H * D * seen(window, keep) / (peaks["bf16_tflops"] * 1e6)
+            return B * seen(window, keep) * (key_heads + value_heads) * D * 2 / (peaks["hbm_gbs"] * 1e3)
+
+        heads = lat["heads"]
+        D = -(-(lat["kv_rank"] + lat["rot_dim"]) // 16) * 16
+        frac(f"latent_attention_{name}", attention(heads, 1, D, shared=True), attention_roof(heads, D, 1, 0))
+        frac(f"delilorn_latent_attention_{name}", attention(heads, 1, D, sinks=torch.randn(heads, device=dev), shared=True),
+             attention_roof(heads, D, 1, 0))
+        H2, G2 = two["heads"], two["kv_heads"]
+        combine = lambda o: ops.map_difference(o, H2, G2, 128, 0.8, 1e-6, 0.5)
+        frac(f"two_map_attention_{name}", attention(2 * H2, 2 * G2, 128, softcap=two["softcap"], after=combine),
+             attention_roof(2 * H2, 128, 2 * G2, G2))
+        frac(f"two_map_attention_kernel_alone_{name}", attention(2 * H2, 2 * G2, 128, softcap=two["softcap"]),
+             attention_roof(2 * H2, 128, 2 * G2, G2))
+        frac(f"attention_as_many_heads_{name}", attention(2 * H2, 2 * G2, 128), attention_roof(2 * H2, 128, 2 * G2, 2 * G2))
+        Gw = win["kv_heads"]
+        frac(f"delilorn_window_attention_{name}", attention(heads, Gw, 128, win["mask"]["size"], win["mask"]["keep_first"]),
+             attention_roof(heads, 128, Gw, Gw, win["mask"]["size"], win["mask"]["keep_first"]))
+        # what stands before the attention kernel: norm of q and k per map, rotation, the maps' rows, keys and value copies
+        qkv = torch.randn(T, (2 * H2 + 2 * G2) * 128 + G2 * 128, device=dev).to(bf)
+        kc = torch.zeros(B * pages_per + 1, 2 * G2, page, 128, device=dev, dtype=bf)
+        vc = torch.zeros_like(kc)
+        slots = torch.cat([table[b, (s + torch.arange(m, device=dev)) // page] * page + (s + torch.arange(m, device=dev)) % page
+                           for b, (s, m) in enumerate(zip(starts, lengths))]).int()
+        positions = torch.cat([torch.arange(s, s + m) for s, m in zip(starts, lengths)]).int().to(dev)
+        from tinyserve_b200.parts.rotary import Rotary
+        cos, sin = Rotary.tables(64, 2.5e5, CONTEXT)
+        rotary = type("R", (), {"cos": cos.to(dev), "sin": sin.to(dev), "rotary_dim": 64, "interleaved": False})()
+        wq = torch.ones(128, device=dev)
+        q_end, k_end = 2 * H2 * 128, (2 * H2 + 2 * G2) * 128
+        frac(f"two_map_norm_rotary_cache_write_{name}", timed(lambda: ops.rope_unit_kvwrite(
+            qkv[:, :q_end], qkv[:, q_end:k_end], qkv[:, k_end:], positions, 2 * H2, 2 * G2, 128, 128, 128, rotary=rotary,
+            k_cache=kc, v_cache=vc, slot_mapping=slots, page_size=page, q_weight=wq, k_weight=wq, pre_eps=1e-6, maps=2)),
+            T * ((2 * H2 + 2 * G2 + G2) * 128 * 2 + (2 * H2 + 4 * G2) * 128 * 2) / (peaks["hbm_gbs"] * 1e3))
+        # (the like kernel of Delilorn's window attention: as many heads, rotation and cache write alone)
+        qkv1 = torch.randn(T, (heads + 2 * Gw) * 128, device=dev).to(bf)
+        kc1 = torch.zeros(B * pages_per + 1, Gw, page, 128, device=dev, dtype=bf)
+        vc1 = torch.zeros_like(kc1)
+        frac(f"delilorn_rotary_cache_write_{name}", timed(lambda: ops.rope_unit_kvwrite(
+            qkv1[:, :heads * 128], qkv1[:, heads * 128:(heads + Gw) * 128], qkv1[:, (heads + Gw) * 128:], positions, heads, Gw,
+            128, 128, 128, rotary=rotary, k_cache=kc1, v_cache=vc1, slot_mapping=slots, page_size=page)),
+            T * (heads + 2 * Gw) * 128 * 2 * 2 / (peaks["hbm_gbs"] * 1e3))
+        # the experts, and the dense feed-forward
+        E, top = moe["router"]["experts"], moe["router"]["top"]
+        ffe, ffd, ff = moe["expert"]["ff"], moe_d["expert"]["ff"], dense["ff"]
+        mine = MixtureOfExperts(width, ffe, E, top, activation="bounded_swish_gated", router="softmax_chosen", limit=7.0, router_bias=True)
+        mine.bind({"router.weight": (torch.randn(E, width, device=dev) * 0.1).to(bf), "router.bias": torch.randn(E, device=dev),
+                   "up.weight": (torch.randn(E * 2 * ffe, width, device=dev) * 0.02).to(bf),
+                   "down.weight": (torch.randn(E * width, ffe, device=dev) * 0.02).to(bf)})
+        theirs = MixtureOfExperts(width, ffd, E, top)
+        theirs.bind({"router.weight": (torch.randn(E, width, device=dev) * 0.1).to(bf),
+                     "up.weight": (torch.randn(E * ffd, width, device=dev) * 0.02).to(bf),
+                     "down.weight": (torch.randn(E * width, ffd, device=dev) * 0.02).to(bf)})
+        h = torch.randn(T, width, device=dev).to(bf)
+        gate_up = (torch.randn(2 * ff, width, device=dev) * 0.02).to(bf)
+        down = (torch.randn(width, ff, device=dev) * 0.02).to(bf)
+        block = ops.GATED_BLOCK if ff % ops.GATED_BLOCK == 0 else 0
+        us_mine = timed(lambda: ops.materialize(mine.forward(h, None)))
+        us_theirs = timed(lambda: ops.materialize(theirs.forward(h, None)))
+        us_dense = timed(lambda: ops.materialize(ops.linear(ops.gated_linear(h, gate_up, "bounded_swish", block, 7.0), down)))
+        us_silu = timed(lambda: ops.materialize(ops.linear(ops.gated_linear(h, gate_up, "silu", block), down)))
+        if T > B:
+            frac(f"experts_{name}", us_mine, 6.0 * T * top * width * ffe / (peaks["bf16_tflops"] * 1e6))
+            frac(f"delilorn_experts_{name}", us_theirs, 4.0 * T * top * width * ffd / (peaks["bf16_tflops"] * 1e6))
+            frac(f"dense_feed_forward_{name}", us_dense, 6.0 * T * width * ff / (peaks["bf16_tflops"] * 1e6))
+            frac(f"qwen3_feed_forward_{name}", us_silu, 6.0 * T * width * ff / (peaks["bf16_tflops"] * 1e6))
+        else:
+            frac(f"experts_{name}", us_mine, 3.0 * E * width * ffe * 2 / (peaks["hbm_gbs"] * 1e3))
+            frac(f"delilorn_experts_{name}", us_theirs, 2.0 * E * width * ffd * 2 / (peaks["hbm_gbs"] * 1e3))
+            frac(f"dense_feed_forward_{name}", us_dense, 3.0 * width * ff * 2 / (peaks["hbm_gbs"] * 1e3))
+            frac(f"qwen3_feed_forward_{name}", us_silu, 3.0 * width * ff * 2 / (peaks["hbm_gbs"] * 1e3))
+        # the stream: output times its factors, added and normed; Delilorn: output normed, added and normed
+        res = torch.randn(T, width, device=dev)
+        y = torch.randn(T, width, device=dev).to(bf)
+        wn, ls = torch.ones(width, device=dev), torch.ones(width, device=dev).to(bf)
+        roof = T * width * (8 + 2 + 2) / (peaks["hbm_gbs"] * 1e3)
+        frac(f"scaled_add_rmsnorm_{name}", timed(lambda: ops.add_rmsnorm(ops.ColumnScaled(y, ls), res, wn, 1e-6, bf)), roof)
+        frac(f"delilorn_normed_add_rmsnorm_{name}", timed(lambda: ops.normed_add_rmsnorm(ops.NormedAddend(y, wn, 1e-6), res, wn, 1e-6, bf)), roof)
+        first = torch.randn(T, width, device=dev)
+        frac(f"stream_add_{name}", timed(lambda: ops.stream_add_(res, ops.ColumnScaled(y, ls), first)),
+             T * width * (8 + 2 + 4) / (peaks["hbm_gbs"] * 1e3))
+    return out
+
+
 # design -> (its shapes and those of the model beside it, its kernel table, the name of the model beside it)
 ARCH_BENCHES = {"dudatar": (dudatar_shapes, kernel_table, "qwen3"), "delilorn": (delilorn_shapes, delilorn_kernel_table, "qwen3"),
-                "tarivik": (tarivik_shapes, tarivik_kernel_table, "delilorn")}
+                "tarivik": (tarivik_shapes, tarivik_kernel_table, "delilorn"),
+                "babadra": (babadra_shapes, babadra_kernel_table, "delilorn")}
 
 
 def arch_main(a) -> int:
-    """``--arch dudatar`` / ``--arch delilorn``: the design beside Qwen3 at equal size; ``--arch tarivik``: beside
-    Delilorn, the closest design (experts, matrix-state mixers, attention with a sink).  One JSON line."""
+    """``--arch dudatar`` / ``--arch delilorn``: the design beside Qwen3 at equal size; ``--arch tarivik`` and
+    ``--arch babadra``: beside Delilorn, the closest design (experts, latent attention, matrix-state mixers).  One
+    JSON line."""
     import torch
     from tinyserve_b200 import LLM
     from tinyserve_b200.config import config_from_dict
@@ -831,10 +1002,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the 0.6B burst, the 32B run and the long-context decode")
-    ap.add_argument("--arch", choices=["qwen3", "dudatar", "delilorn", "tarivik"], default="qwen3",
+    ap.add_argument("--arch", choices=["qwen3", "dudatar", "delilorn", "tarivik", "babadra"], default="qwen3",
                     help="dudatar, delilorn: measure that design beside Qwen3 at equal size instead of the default workload; "
-                         "tarivik: beside Delilorn")
-    ap.add_argument("--sizes", default="2048,4096", help="--arch dudatar / delilorn / tarivik: model widths to measure")
+                         "tarivik, babadra: beside Delilorn")
+    ap.add_argument("--sizes", default="2048,4096", help="--arch dudatar / delilorn / tarivik / babadra: model widths to measure")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_main(a)

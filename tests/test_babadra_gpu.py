@@ -98,11 +98,15 @@ def test_factors_on_a_product_that_is_still_partial_tiles(M, K, N):
             ops.stream_add_(residual, scaled, on_device(first, torch.float32))
             assert (residual.double().cpu() - (stream + first)).abs().max() <= 1e-5 * stream.abs().max()
             continue
-        out = ops.add_rmsnorm(scaled, residual, on_device(1 + w, torch.float32), 1e-6, torch.bfloat16, scaled_ok=True)
-        assert isinstance(out, torch.Tensor)
         want = plain.norm_around_zero(stream, w, 1e-6)
-        assert (residual.double().cpu() - stream).abs().max() <= 1e-5 * stream.abs().max()
-        assert (out.double().cpu() - want).abs().max() <= 1e-2 * want.abs().max()
+        for scaled_ok in (False, True):
+            # (a reader that only multiplies takes rows without their norm factor: the product then adds to the
+            # residual itself, factors included)
+            residual = on_device(r, torch.float32)
+            out = ops.add_rmsnorm(scaled, residual, on_device(1 + w, torch.float32), 1e-6, torch.bfloat16, scaled_ok=scaled_ok)
+            assert isinstance(out, ops.ScaledRows if scaled_ok else torch.Tensor)
+            assert (residual.double().cpu() - stream).abs().max() <= 1e-5 * stream.abs().max()
+            assert (ops.materialize(out).double().cpu() - want).abs().max() <= 1e-2 * want.abs().max()
 
 
 def test_embedding_rows_are_scaled_in_32_bit():
@@ -153,6 +157,21 @@ def test_dense_feed_forward_against_the_plain_one(dtype, tol, T, width, ff):
     assert (got.double().cpu() - want).abs().max() <= tol * want.abs().max()
 
 
+@pytest.mark.parametrize("M,K,N", [(7, 256, 384), (16, 512, 2048), (2048, 4096, 512)])
+def test_bounded_gate_in_the_epilogue_of_the_products(M, K, N):
+    """A few bfloat16 rows and a long prompt portion: the product applies the gate itself; the same
+    numbers, to a rounding, as the product followed by the activation kernel."""
+    from tinyserve_b200.kernels import ops
+    x, W = on_device(draws(M, K, seed=1), torch.bfloat16), on_device(draws(N, K, seed=2, scale=0.05), torch.bfloat16)
+    launches = ops.launch_count()
+    fused = ops.gated_linear(x, W, "bounded_swish", ops.GATED_BLOCK, 0.7)
+    assert ops.launch_count() - launches == 1 or ops.gemm_splits(M, N, K) > 1, "one kernel where the product is not cut along K"
+    apart = ops.gated_activation(ops.materialize(ops.linear(x, W)), "bounded_swish", ops.GATED_BLOCK, 0.7)
+    assert fused.shape == (M, N // 2)
+    assert (fused.double() - apart.double()).abs().max() <= 1e-2 * apart.double().abs().max()
+    assert apart.double().abs().max() > 0.5
+
+
 @pytest.mark.parametrize("E,top", [(8, 2), (5, 5), (1, 1), (40, 7), (3, 1)])
 def test_router_weights_are_the_softmax_over_the_chosen_logits(E, top):
     from tinyserve_b200.kernels import ops
@@ -163,6 +182,10 @@ def test_router_weights_are_the_softmax_over_the_chosen_logits(E, top):
     want = torch.zeros_like(z).scatter(1, idx, torch.softmax(best, -1))
     assert (gates - want).abs().max() < 1e-6
     assert ((gates.sum(-1) - 1).abs() < 1e-6).all() and ((gates > 0).sum(-1) <= top).all()
+    b = draws(E, seed=9, scale=2.0)
+    biased = ops.moe_route(on_device(z, torch.float32), top, renormalize=True, bias=on_device(b, torch.float32)).double().cpu()
+    best, at = torch.topk(z + b, top, -1)
+    assert (biased - torch.zeros_like(z).scatter(1, at, torch.softmax(best, -1))).abs().max() < 1e-6
     kept = ops.moe_route(on_device(z, torch.float32), top).double().cpu()
     assert (kept - torch.zeros_like(z).scatter(1, idx, torch.softmax(z, -1).gather(1, idx))).abs().max() < 1e-6, "the other form stays"
 
@@ -287,7 +310,7 @@ def _two_map_case(H, G, n, nv, rot, scale, cap, diff, kv_lens, seed):
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 4e-2)])
 @pytest.mark.parametrize("H,G,n,nv,page", [(4, 2, 16, 32, 8), (3, 1, 48, 16, 16), (2, 2, 24, 16, 4), (6, 3, 20, 40, 16),
                                            (4, 1, 64, 64, 32), (2, 1, 128, 128, 64), (2, 2, 32, 128, 16)])
-@pytest.mark.parametrize("cap", [None, 3.0])
+@pytest.mark.parametrize("cap", [None, 3.0, 40.0])
 def test_two_score_maps_over_the_same_values(dtype, tol, H, G, n, nv, page, cap):
     """q/k norm with shared weights, rotation of a part of every map, the maps' rows and the copies of
     the values as the attention kernels want them, capped scores, the maps' difference normed per head:

@@ -90,6 +90,7 @@ struct PairParams {
   float x_eps;
   VecParam bias;
   int gated_act;          // 0: off, else activation code + 1; out [M, N / 2]
+  float gated_limit;      // the bound of a bounded activation (gated_value)
   float* residual;        // [M, N] float, contiguous
   VecParam norm_w;
   bf16* hprime;           // [M, N]
@@ -403,7 +404,7 @@ __device__ __forceinline__ bool epilogue_half(const PairParams& p, const Segment
         take(h * 4 + sub, 0, gt);
         take(h * 4 + 2 + sub, 1, up);
 #pragma unroll
-        for (int e = 0; e < CHUNK; ++e) gt[e] = activate(gt[e] * row_scale, act) * (up[e] * row_scale);
+        for (int e = 0; e < CHUNK; ++e) gt[e] = gated_value(gt[e] * row_scale, up[e] * row_scale, act, p.gated_limit);
         tile_write_bf16(ost_tile(h), r_in, sub * 4, gt);
         if (partial) epi_barrier(g);                            // the tiles that `take` went through are read
       }
@@ -745,7 +746,8 @@ TS_EXPORT long long ts_gemm_pair_scratch(int M, int N, int K, int pairs, int hal
 // x_sumsq [x_tiles][x_stride] != nullptr: the rows of x lack their RMSNorm factor; row m of the
 // result is scaled by rsqrt(sum_t x_sumsq[t][m] / K + x_eps) (plain and gated forms).
 // gated_act != 0: the rows of w alternate in blocks of 64, gate rows then the matching up rows;
-// out [M, N / 2] bfloat16 = act(gate) * up with act = gated_act - 1 (0 SiLU, 1 GELU-tanh); N a multiple of 128.
+// out [M, N / 2] bfloat16 = act(gate) * up with act = gated_act - 1 (0 SiLU, 1 GELU-tanh, 2 the bounded form of
+// gated_value with gated_limit as its bound); N a multiple of 128.
 // residual != nullptr (out unused): residual [M, N] (float, contiguous) += x w^T; hprime [M, N]
 // (bfloat16) = residual * norm_w; sumsq_out [N / 128 rounded up][sumsq_stride >= M] = the sums of
 // residual^2 over each 128 columns.
@@ -754,7 +756,7 @@ TS_EXPORT int ts_gemm_pair(const void* x, const void* w, void* out, int M, int N
                            int x_tiles, int x_stride, float x_eps, int gated_act, float* residual,
                            const void* norm_w, int norm_w_is_f32, void* hprime, float* sumsq_out, int sumsq_stride,
                            float* scratch, long long scratch_floats, int* counters, int num_counters, int pairs,
-                           int halves, cudaStream_t stream) {
+                           int halves, float gated_limit, cudaStream_t stream) {
   TS_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_pair: empty operand");
   TS_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && N % 8 == 0,
              "gemm_pair: N, K and the leading dimensions must be multiples of 8, got N=%d K=%d", N, K);
@@ -763,7 +765,7 @@ TS_EXPORT int ts_gemm_pair(const void* x, const void* w, void* out, int M, int N
   TS_REQUIRE(pairs >= 1 && pairs <= 1024, "gemm_pair: pairs out of range");
   TS_REQUIRE(residual != nullptr || (out != nullptr && ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0),
              "gemm_pair: the output must be 16-byte aligned with a leading dimension that is a multiple of 8");
-  TS_REQUIRE(gated_act == 0 || (gated_act <= 2 && !out_f32 && residual == nullptr && bias == nullptr && N % 128 == 0),
+  TS_REQUIRE(gated_act == 0 || (gated_act <= ACT_COUNT && (gated_act - 1 != ACT_BOUNDED_SWISH || gated_limit > 0.f) && !out_f32 && residual == nullptr && bias == nullptr && N % 128 == 0),
              "gemm_pair: the gated form takes a bfloat16 output, no bias and whole blocks of 64 gate and 64 up rows");
   TS_REQUIRE(residual == nullptr || (norm_w && hprime && sumsq_out && sumsq_stride >= M && bias == nullptr && x_sumsq == nullptr
                                      && !out_f32 && (reinterpret_cast<uintptr_t>(residual) & 15) == 0 && (reinterpret_cast<uintptr_t>(hprime) & 15) == 0),
@@ -782,6 +784,7 @@ TS_EXPORT int ts_gemm_pair(const void* x, const void* w, void* out, int M, int N
   p.x_sumsq = x_sumsq; p.x_tiles = x_tiles; p.x_stride = x_stride; p.x_eps = x_eps;
   p.bias = VecParam{bias, bias_is_f32};
   p.gated_act = gated_act;
+  p.gated_limit = gated_limit;
   p.residual = residual; p.norm_w = VecParam{norm_w, norm_w_is_f32};
   p.hprime = static_cast<bf16*>(hprime); p.sumsq_out = sumsq_out; p.sumsq_stride = sumsq_stride;
   CUtensorMap mx, mw;

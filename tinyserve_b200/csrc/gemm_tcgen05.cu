@@ -59,7 +59,9 @@ struct GemmParams {
   // Gated form (no K cuts, up to 64 tokens): the weight rows alternate in blocks of 64, gate rows
   // then the matching up rows, so a 128-row tile holds both; out [M, N / 2] = act(gate) * up.
   int gated_act;        // 0: off; else the activation's code + 1
+  float gated_limit;    // the bound of a bounded activation (gated_value)
   VecParam bias;        // [N] added to every token's result (plain output only); ptr null: none
+  VecParam res_scale;   // residual form: [N] factors on the result before it joins the residual; ptr null: none
 };
 constexpr int SUMSQ_STRIDE = 16;     // tokens of the residual form (one token tile of 16)
 
@@ -240,6 +242,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
     const float wn = (epi && n < p.N) ? p.norm_w[n] : 0.f;
+    const float rs = (epi && n < p.N && p.res_scale.ptr != nullptr) ? p.res_scale[n] : 1.f;
     cluster_arrive();
     cluster_wait();
     for (int j = split; j < TILE_T && t0 + j < p.M; j += p.splits) {
@@ -254,7 +257,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int s = 0; s < 8; ++s)
           if (s < p.splits) sum += part[s];
-        const float v = p.residual[(size_t)m * p.N + n] + sum;
+        const float v = p.residual[(size_t)m * p.N + n] + sum * rs;
         p.residual[(size_t)m * p.N + n] = v;
         p.hprime[(size_t)m * p.N + n] = __float2bfloat16_rn(v * wn);
         sq = v * v;
@@ -294,7 +297,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const int m = t0 + i;
           if (m < p.M)
             static_cast<bf16*>(p.out)[(size_t)m * p.ldc + col] =
-                __float2bfloat16_rn(activate(acc[i], p.gated_act - 1) * up[threadIdx.x * (TILE_T + 1) + i]);
+                __float2bfloat16_rn(gated_value(acc[i], up[threadIdx.x * (TILE_T + 1) + i], p.gated_act - 1, p.gated_limit));
         }
       }
     }
@@ -446,7 +449,8 @@ namespace {
 int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, long long ldx, long long ldw,
                long long ldc, int out_f32, int splits, float* partials, int* counters, const float* x_sumsq,
                int x_tiles, float x_eps, float* residual, const void* norm_w, int norm_w_is_f32, void* hprime,
-               float* sumsq_out, int gated_act, const void* bias, int bias_is_f32, cudaStream_t stream);
+               float* sumsq_out, int gated_act, const void* bias, int bias_is_f32, float gated_limit,
+               const void* res_scale, int res_scale_is_f32, cudaStream_t stream);
 }
 
 // bias: [N] float or bfloat16 (bias_is_f32), added to every token's result; needs an output
@@ -456,7 +460,7 @@ TS_EXPORT int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, in
                               int* counters, const void* bias, int bias_is_f32, cudaStream_t stream) {
   TS_REQUIRE(bias == nullptr || out != nullptr, "gemm_tcgen05: a bias needs an output, not partial tiles only");
   return gemm_tiled(x, w, out, M, N, K, ldx, ldw, ldc, out_f32, splits, partials, counters, nullptr, 0, 0.f,
-                    nullptr, nullptr, 0, nullptr, nullptr, 0, bias, bias_is_f32, stream);
+                    nullptr, nullptr, 0, nullptr, nullptr, 0, bias, bias_is_f32, 0.f, nullptr, 0, stream);
 }
 
 // The same product with extras.  The first two are for up to 16 tokens.
@@ -469,28 +473,33 @@ TS_EXPORT int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, in
 // over each 128 columns, for the product that takes hprime as its x.
 // gated_act != 0 (up to 64 tokens, splits == 1, bfloat16 out [M, N / 2], ldc its leading
 // dimension, N a multiple of 128): the rows of w alternate in blocks of 64, gate rows then the
-// matching up rows; out = act(gate) * up with act = gated_act - 1 (0 SiLU, 1 GELU-tanh).
+// matching up rows; out = act(gate) * up with act = gated_act - 1 (0 SiLU, 1 GELU-tanh, 2 the
+// bounded form of gated_value with gated_limit as its bound).
+// res_scale (residual form; [N] float or bfloat16, or nullptr): residual += (x w^T) * res_scale.
 TS_EXPORT int ts_gemm_tcgen05_fused(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                                     long long ldw, long long ldc, int out_f32, int splits, float* partials,
                                     int* counters, const float* x_sumsq, int x_tiles, float x_eps,
                                     float* residual, const void* norm_w, int norm_w_is_f32, void* hprime,
-                                    float* sumsq_out, int gated_act, cudaStream_t stream) {
+                                    float* sumsq_out, int gated_act, float gated_limit, const void* res_scale,
+                                    int res_scale_is_f32, cudaStream_t stream) {
   TS_REQUIRE((x_sumsq == nullptr && residual == nullptr) || M <= SUMSQ_STRIDE,
              "gemm_tcgen05: the scaled-rows and residual forms take up to %d tokens, got %d", SUMSQ_STRIDE, M);
-  TS_REQUIRE(gated_act == 0 || (gated_act <= 2 && M <= 64 && splits == 1 && out && !out_f32 && !residual && N % 128 == 0),
+  TS_REQUIRE(gated_act == 0 || (gated_act <= ACT_COUNT && (gated_act - 1 != ACT_BOUNDED_SWISH || gated_limit > 0.f) && M <= 64 && splits == 1 && out && !out_f32 && !residual && N % 128 == 0),
              "gemm_tcgen05: the gated form takes up to 64 tokens, no K cuts, a bfloat16 output and whole 128-row tiles");
   TS_REQUIRE(x_sumsq == nullptr || x_tiles > 0, "gemm_tcgen05: sums of squares without their tile count");
   TS_REQUIRE(residual == nullptr || (norm_w && hprime && sumsq_out && splits <= 8),
              "gemm_tcgen05: the residual form needs the norm's weight, both outputs and at most 8 cuts");
   return gemm_tiled(x, w, out, M, N, K, ldx, ldw, ldc, out_f32, splits, partials, counters, x_sumsq, x_tiles,
-                    x_eps, residual, norm_w, norm_w_is_f32, hprime, sumsq_out, gated_act, nullptr, 0, stream);
+                    x_eps, residual, norm_w, norm_w_is_f32, hprime, sumsq_out, gated_act, nullptr, 0, gated_limit,
+                    residual ? res_scale : nullptr, res_scale_is_f32, stream);
 }
 
 namespace {
 int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, long long ldx, long long ldw,
                long long ldc, int out_f32, int splits, float* partials, int* counters, const float* x_sumsq,
                int x_tiles, float x_eps, float* residual, const void* norm_w, int norm_w_is_f32, void* hprime,
-               float* sumsq_out, int gated_act, const void* bias, int bias_is_f32, cudaStream_t stream) {
+               float* sumsq_out, int gated_act, const void* bias, int bias_is_f32, float gated_limit,
+               const void* res_scale, int res_scale_is_f32, cudaStream_t stream) {
   TS_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: empty operand");
   TS_REQUIRE(M <= 65535 * 128, "gemm_tcgen05: too many rows");
   TS_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: K and the leading dimensions must be multiples of 8 (16-byte rows for TMA), got K=%d", K);
@@ -509,7 +518,9 @@ int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, lon
   p.residual = residual; p.norm_w = VecParam{norm_w, norm_w_is_f32};
   p.hprime = static_cast<bf16*>(hprime); p.sumsq_out = sumsq_out;
   p.gated_act = gated_act;
+  p.gated_limit = gated_limit;
   p.bias = VecParam{bias, bias_is_f32};
+  p.res_scale = VecParam{res_scale, res_scale_is_f32};
   dim3 grid((N + TILE_N - 1) / TILE_N, (M + tile_t - 1) / tile_t, splits);
   switch (tile_t) {
     case 16: return launch<16>(mw, mx, p, grid, stream);

@@ -157,16 +157,17 @@ __global__ void gate_heads_kernel(const T* __restrict__ x, const T* __restrict__
 // ------------------------------------------------------------------ mixture of experts
 // a warp per token: probabilities of all experts, the `top` largest kept (ties: the lower number)
 // one warp, one token: z [E] logits -> g [E] (global or shared memory)
+// `bias` [E] (or null) is added to the logits first, in 32-bit
 __device__ __forceinline__ void route_token(const float* __restrict__ z, float* g, int E, int top, int lane,
-                                            int renorm = 0) {
+                                            int renorm = 0, const float* __restrict__ bias = nullptr) {
   float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e] + (bias ? bias[e] : 0.f));
   mx = warp_max(mx);
   float sum = 0.f;
-  for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
+  for (int e = lane; e < E; e += 32) sum += expf(z[e] + (bias ? bias[e] : 0.f) - mx);
   sum = warp_sum(sum);
   const float inv = 1.f / sum;
-  for (int e = lane; e < E; e += 32) g[e] = -expf(z[e] - mx) * inv;      // negative: not chosen yet
+  for (int e = lane; e < E; e += 32) g[e] = -expf(z[e] + (bias ? bias[e] : 0.f) - mx) * inv;      // negative: not chosen yet
   __syncwarp();
   for (int k = 0; k < top; ++k) {
     float best = 0.f;                 // the largest probability among those not chosen yet
@@ -278,12 +279,22 @@ __global__ void moe_route_scored_kernel(const float* __restrict__ logits, const 
 }
 
 // out[r, e * ff + j] = gated_value(a[r, e * 2 ff + j], a[r, e * 2 ff + ff + j]) * gates[r, e] (gates null: 1)
+// With `logits` (and top > 0) in place of gates every block routes its row itself first (its first
+// warp, into shared memory), as ts_moe_route does: one launch for the router's softmax, its choice
+// and the activation.
 template <typename T>
 __global__ void moe_gated_activate_kernel(const T* __restrict__ a, const float* __restrict__ gates, int E, int ff,
-                                          T* __restrict__ out, int act, float limit) {
+                                          T* __restrict__ out, int act, float limit, const float* __restrict__ logits,
+                                          const float* __restrict__ bias, int top, int renorm) {
+  extern __shared__ float routed[];      // [E] when the kernel routes
   pdl_trigger();
   pdl_wait();
   const size_t r = blockIdx.x;
+  if (logits) {
+    if (threadIdx.x < 32) route_token(logits + r * E, routed, E, top, threadIdx.x, renorm, bias);
+    __syncthreads();
+    gates = routed - r * E;              // the loop below indexes gates[r * E + e]
+  }
   const T* row = a + r * (size_t)E * 2 * ff;
   T* dst = out + r * (size_t)E * ff;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < E * ff; i += gridDim.y * blockDim.x) {
@@ -299,13 +310,13 @@ __global__ void moe_gated_activate_kernel(const T* __restrict__ a, const float* 
 }
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, float* __restrict__ gates, int num_tokens, int E, int top,
-                                 int renorm) {
+                                 int renorm, const float* __restrict__ bias) {
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + warp;
   if (t >= num_tokens) return;
-  route_token(logits + (size_t)t * E, gates + (size_t)t * E, E, top, lane, renorm);
+  route_token(logits + (size_t)t * E, gates + (size_t)t * E, E, top, lane, renorm, bias);
 }
 
 // 16 bytes of a row as floats and back
@@ -588,9 +599,10 @@ TS_EXPORT int ts_gate_heads(int dtype, const void* x, const void* gate, long lon
   return 0;
 }
 
-TS_EXPORT int ts_moe_route(const float* logits, float* gates, int num_tokens, int E, int top, int renorm, cudaStream_t stream) {
+TS_EXPORT int ts_moe_route(const float* logits, float* gates, int num_tokens, int E, int top, int renorm, const float* bias,
+                           cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && E > 0 && top > 0 && top <= E && logits && gates, "moe_route: %d of %d experts", top, E);
-  TS_LAUNCH("moe_route", moe_route_kernel, (num_tokens + 3) / 4, 128, 0, stream, logits, gates, num_tokens, E, top, renorm);
+  TS_LAUNCH("moe_route", moe_route_kernel, (num_tokens + 3) / 4, 128, 0, stream, logits, gates, num_tokens, E, top, renorm, bias);
   return 0;
 }
 
@@ -608,17 +620,21 @@ TS_EXPORT int ts_moe_route_scored(const float* logits, const float* correction, 
 }
 
 TS_EXPORT int ts_moe_gated_activate(int dtype, const void* a, const float* gates, int rows, int E, int ff, void* out,
-                                    int act, float limit, cudaStream_t stream) {
+                                    int act, float limit, const float* logits, const float* bias, int top, int renorm,
+                                    cudaStream_t stream) {
   TS_REQUIRE(rows > 0 && E > 0 && ff > 0 && a && out, "moe_gated_activate: empty input");
+  TS_REQUIRE(!(gates && logits) && (logits == nullptr || (top > 0 && top <= E && E <= 8192)), "moe_gated_activate: gates or logits with top of %d experts", E);
+  const size_t smem = logits ? (size_t)E * sizeof(float) : 0;
   TS_REQUIRE(act >= 0 && act < ACT_COUNT && (act != ACT_BOUNDED_SWISH || limit > 0.f), "moe_gated_activate: activation %d", act);
   // a row's columns over several blocks (four elements a thread), so that a step of few rows still fills the SMs
   const long long tiles = ((long long)E * ff + 1023) / 1024;
   const dim3 grid(rows, (unsigned)(tiles < 64 ? tiles : 64));
   if (dtype == TS_F32)
-    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<float>, grid, 256, 0, stream, (const float*)a, gates, E, ff, (float*)out, act, limit);
+    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<float>, grid, 256, smem, stream, (const float*)a, gates, E, ff, (float*)out, act, limit,
+              logits, bias, top, renorm);
   else if (dtype == TS_BF16)
-    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)a, gates, E, ff,
-              (__nv_bfloat16*)out, act, limit);
+    TS_LAUNCH("moe_gated_activate", moe_gated_activate_kernel<__nv_bfloat16>, grid, 256, smem, stream, (const __nv_bfloat16*)a, gates, E, ff,
+              (__nv_bfloat16*)out, act, limit, logits, bias, top, renorm);
   else return ts_fail("moe_gated_activate: unknown dtype %d", dtype);
   return 0;
 }

@@ -377,7 +377,7 @@ def _tile_t(M):
     return 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
 
 
-def _linear_tcgen05(x, weight, out_float32, splits=None, partials_only=False, scale=None, gated=0, bias=None):
+def _linear_tcgen05(x, weight, out_float32, splits=None, partials_only=False, scale=None, gated=0, bias=None, limit=0.0):
     """``scale``: the ScaledRows whose ``data`` is ``x``; ``gated``: activation code + 1 of the
     gated epilogue (out [M, N / 2]); ``bias`` [N]: added in the epilogue (not with the others)."""
     M, K = x.shape
@@ -403,7 +403,7 @@ def _linear_tcgen05(x, weight, out_float32, splits=None, partials_only=False, sc
             _ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(x.stride(0)),
             c_longlong(weight.stride(0)), c_longlong(out_cols), c_int(1 if out_float32 else 0), c_int(splits),
             _ptr(partials), _ptr(counters), *(scale.args() if scale is not None else _NO_SCALE), None, None,
-            c_int(0), None, None, c_int(gated), _stream()))
+            c_int(0), None, None, c_int(gated), c_float(limit), None, c_int(0), _stream()))
     else:
         _check(lib, lib.ts_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K),
                                         c_longlong(x.stride(0)), c_longlong(weight.stride(0)), c_longlong(N),
@@ -458,7 +458,7 @@ def _pair_workspace(lib, M, N, K, pairs, halves, out_float32, device):
     return have
 
 
-def _linear_pair(x, weight, out_float32=False, bias=None, scale=None, gated=0, residual=None, norm_weight=None,
+def _linear_pair(x, weight, out_float32=False, bias=None, scale=None, gated=0, limit=0.0, residual=None, norm_weight=None,
                  pairs=None, halves=0):
     """The product for many tokens on pairs of SMs (csrc/gemm_pair_tcgen05.cu).  Plain: returns
     out [M, N]; ``bias`` [N]; ``scale`` the ScaledRows whose ``data`` is ``x``.  ``gated``:
@@ -487,7 +487,7 @@ def _linear_pair(x, weight, out_float32=False, bias=None, scale=None, gated=0, r
         c_int(gated), _ptr(residual), _ptr(norm_weight),
         c_int(_vec_flag(norm_weight, torch.bfloat16) if norm_weight is not None else 0), _ptr(hprime), _ptr(sumsq),
         c_int(stride), _ptr(scratch), c_longlong(scratch.numel()), _ptr(counters), c_int(counters.numel()),
-        c_int(pairs), c_int(halves), _stream()))
+        c_int(pairs), c_int(halves), c_float(limit), _stream()))
     if residual is not None:
         return hprime, sumsq
     return out
@@ -588,9 +588,10 @@ def embed_lookup(table, ids, slot_tokens=None, scale=1.0):
     return out
 
 
-def _product_add_residual(pending, residual, weight, eps):
-    """The residual form of the tcgen05 product: residual += x w^T inside the product's kernel;
-    returns the ScaledRows of the new residual for the norm with ``weight``."""
+def _product_add_residual(pending, residual, weight, eps, x_scale=None):
+    """The residual form of the tcgen05 product: residual += x w^T (times one factor per column
+    with ``x_scale``) inside the product's kernel; returns the ScaledRows of the new residual for
+    the norm with ``weight``."""
     x, w = pending.x, pending.weight
     M, K = x.shape
     N = w.shape[0]
@@ -604,7 +605,8 @@ def _product_add_residual(pending, residual, weight, eps):
     _check(lib, lib.ts_gemm_tcgen05_fused(
         _ptr(x), _ptr(w), None, c_int(M), c_int(N), c_int(K), c_longlong(x.stride(0)), c_longlong(w.stride(0)),
         c_longlong(N), c_int(0), c_int(pending.splits()), None, None, *_NO_SCALE, _ptr(residual), _ptr(weight),
-        c_int(_vec_flag(weight, torch.bfloat16)), _ptr(hprime), _ptr(sumsq), c_int(0), _stream()))
+        c_int(_vec_flag(weight, torch.bfloat16)), _ptr(hprime), _ptr(sumsq), c_int(0), c_float(0.0), _ptr(x_scale),
+        c_int(_vec_flag(x_scale, torch.bfloat16) if x_scale is not None else 0), _stream()))
     return ScaledRows(hprime, sumsq, tiles, eps)
 
 
@@ -618,6 +620,11 @@ def add_rmsnorm(x, residual, weight, eps, out_dtype, rows=None, scaled_ok=False)
     if isinstance(x, ColumnScaled):
         x, x_scale = x.x, x.scale
         if isinstance(x, PendingProduct):
+            if (scaled_ok and rows is None and out_dtype == torch.bfloat16 and not x.wide and x.shape == tuple(residual.shape)
+                    and residual.dtype == torch.float32 and residual.is_contiguous()
+                    and x_scale.shape == (residual.shape[1],) and x_scale.is_contiguous()):
+                _cuda(residual, weight, x_scale)
+                return _product_add_residual(x, residual, weight, eps, x_scale)
             x = x.partials()
     if isinstance(x, PendingProduct):
         if (scaled_ok and rows is None and out_dtype == torch.bfloat16 and x.shape == tuple(residual.shape)
@@ -690,23 +697,22 @@ def gated_linear(x, weight, activation="silu", block=0, limit=0.0):
     ScaledRows that add_rmsnorm returned."""
     rows = x.data if isinstance(x, ScaledRows) else x
     N, K = weight.shape
-    if activation in BOUNDED_ACTIVATIONS:      # (the products' epilogues know the unbounded activations)
-        return gated_activation(linear(x, weight), activation, block, limit)
+    code, limit = activation_code(activation, limit)
     if (block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
             and rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _pair_ok(rows, weight)
             and (rows.shape[0] >= PAIR_MIN_TOKENS
                  or (rows is x and PAIR_GATED_MIN_TOKENS <= rows.shape[0] <= PAIR_GATED_MAX_TOKENS
                      and K >= PAIR_GATED_MIN_K))):
         _cuda(rows, weight)
-        return _linear_pair(rows, weight, gated=ACTIVATIONS[activation] + 1, scale=x if rows is not x else None)
+        return _linear_pair(rows, weight, gated=code + 1, limit=limit, scale=x if rows is not x else None)
     if (block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
             and rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _tcgen05_ok(rows, weight)
             and rows.shape[0] <= FUSED_MAX_TOKENS          # measured: at 64 tokens the epilogue costs 9 % of the step
             and gemm_splits(rows.shape[0], N, K) == 1):
         _cuda(rows, weight)
-        return _linear_tcgen05(rows, weight, False, splits=1, gated=ACTIVATIONS[activation] + 1,
+        return _linear_tcgen05(rows, weight, False, splits=1, gated=code + 1, limit=limit,
                                scale=x if rows is not x else None)
-    return gated_activation(linear(x, weight), activation, block)
+    return gated_activation(linear(x, weight), activation, block, limit)
 
 
 def qk_norm_rope_kvwrite(qkv, positions, num_heads, num_kv_heads, head_dim, rotary=None,
@@ -1632,18 +1638,21 @@ def batched_matmul(a, b):
 
 
 # ----------------------------------------------------------------------------- mixture of experts
-def moe_route(logits, top, renormalize=False):
+def moe_route(logits, top, renormalize=False, bias=None):
     """float32 [T, E] router logits -> float32 [T, E]: softmax over all experts, the ``top`` largest
     keep their probability as it is, the others become zero.  With ``renormalize`` the kept ones are
-    divided by their sum: the softmax over the chosen logits alone."""
-    _cuda(logits)
+    divided by their sum: the softmax over the chosen logits alone.  ``bias`` (float32 [E]) is added
+    to the logits first."""
+    _cuda(logits, bias)
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape != (logits.shape[1],)):
+        raise TypeError("moe_route: the bias is float32 [experts]")
     if logits.dtype != torch.float32 or not logits.is_contiguous():
         raise TypeError("moe_route: router logits are contiguous float32")
     T, E = logits.shape
     gates = torch.empty_like(logits)
     lib = _latent_moe()
     _check(lib, lib.ts_moe_route(_ptr(logits), _ptr(gates), c_int(T), c_int(E), c_int(top), c_int(1 if renormalize else 0),
-                                 _stream()))
+                                 _ptr(bias), _stream()))
     return gates
 
 
@@ -1909,12 +1918,19 @@ def moe_route_scored(logits, correction, top, groups=1, keep=1):
     return gates
 
 
-def moe_gated_activate(a, gates, num_experts, activation="silu", limit=0.0):
+def moe_gated_activate(a, gates, num_experts, activation="silu", limit=0.0, logits=None, top=0, renormalize=False,
+                       bias=None):
     """a [rows, E * 2 ff] (per expert: gate rows, then up rows) -> [rows, E * ff] =
     act(gate) * up * gates[row, e] (``activation`` as in ``gated_activation``); ``gates`` None: no
-    weight (rows that are sorted by expert)."""
-    _cuda(a, gates)
+    weight (rows that are sorted by expert).  With ``logits`` (float32 [rows, E]) and ``top`` in
+    place of ``gates`` the kernel routes every row itself first, as ``moe_route`` does with the same
+    ``renormalize`` and ``bias``: one launch for softmax, choice and activation."""
+    _cuda(a, gates, logits, bias)
     code, limit = activation_code(activation, limit)
+    if logits is not None and (gates is not None or logits.shape != (a.shape[0], num_experts) or logits.dtype != torch.float32
+                               or not logits.is_contiguous() or not 0 < top <= num_experts
+                               or (bias is not None and (bias.dtype != torch.float32 or bias.shape != (num_experts,)))):
+        raise ValueError("moe_gated_activate: logits are float32 [rows, experts], with top and without gates")
     rows = a.shape[0]
     ff = a.shape[1] // (2 * num_experts)
     if not a.is_contiguous() or a.shape[1] != 2 * ff * num_experts or \
@@ -1923,5 +1939,6 @@ def moe_gated_activate(a, gates, num_experts, activation="silu", limit=0.0):
     out = torch.empty(rows, num_experts * ff, dtype=a.dtype, device=a.device)
     lib = _latent_moe()
     _check(lib, lib.ts_moe_gated_activate(c_int(_dt(a)), _ptr(a), _ptr(gates), c_int(rows), c_int(num_experts), c_int(ff),
-                                          _ptr(out), c_int(code), c_float(limit), _stream()))
+                                          _ptr(out), c_int(code), c_float(limit), _ptr(logits), _ptr(bias), c_int(top),
+                                          c_int(1 if renormalize else 0), _stream()))
     return out

@@ -101,20 +101,24 @@ class MixtureOfExperts(FeedForward):
     def _route(self, logits):
         if self.router == "sigmoid_corrected":
             return ops.moe_route_scored(logits, self.w["correction"], self.top, self.groups, self.keep_groups)
-        return ops.moe_route(logits, self.top, renormalize=self.router == "softmax_chosen")
+        return ops.moe_route(logits, self.top, renormalize=self.router == "softmax_chosen", bias=self.w.get("router.bias"))
 
     def forward(self, h, ctx):
         logits = ops.linear(h, self.w["router.weight"], out_float32=True)
-        if self.router_bias:
+        if self.router_bias and self.router == "sigmoid_corrected":
             ops.add_row_vector_(logits, self.w["router.bias"])
         if (h.dtype == torch.bfloat16 and self.top < self.num_experts and h.shape[0] >= ops.MOE_GROUPED_MIN_TOKENS
                 and self.hidden_size % 8 == 0 and self.intermediate_size % 8 == 0):
             return ops.moe_grouped(h, self._route(logits), self.w["up.weight"], self.w["down.weight"], self.top,
                                    gated=self.gated, activation=self.gate_activation, limit=self.limit)
         a = ops.materialize(ops.linear(h, self.w["up.weight"]))
-        if self.gated:
+        if self.gated and self.router != "sigmoid_corrected":
+            # (routes in the same kernel)
+            a = ops.moe_gated_activate(a, None, self.num_experts, self.gate_activation, self.limit, logits=logits, top=self.top,
+                                       renormalize=self.router == "softmax_chosen", bias=self.w.get("router.bias"))
+        elif self.gated:
             a = ops.moe_gated_activate(a, self._route(logits), self.num_experts, self.gate_activation, self.limit)
-        elif self.router == "softmax":
+        elif self.router == "softmax" and not self.router_bias:
             ops.moe_activate_(a, None, self.num_experts, logits=logits, top=self.top)      # (routes in the same kernel)
         else:
             ops.moe_activate_(a, self._route(logits), self.num_experts)
