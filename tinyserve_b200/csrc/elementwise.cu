@@ -1244,7 +1244,8 @@ __global__ void stream_add_kernel(float* __restrict__ residual, const T* __restr
   pdl_trigger();
   pdl_wait();
   const size_t m = blockIdx.x;
-  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+  // (a row's columns over the blocks of grid.y: few rows still fill the SMs and no thread walks a chain of loads)
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n; c += gridDim.y * blockDim.x) {
     float v = residual[m * n + c];
     const float s = xs.ptr ? xs[c] : 1.f;
     if (ps.base) v += ps.load1((int)m, c) * s;
@@ -1263,8 +1264,10 @@ TS_EXPORT int ts_stream_add(int dtype, float* residual, const void* x, const voi
   PartialSrc ps{partials, splits, n_tiles, t_tiles, tile_t};
   VecParam xs{x_scale, x_scale_is_f32};
   const int threads = n >= 512 ? 256 : 128;
-  if (dtype == TS_F32) TS_LAUNCH("stream_add", stream_add_kernel<float>, num_rows, threads, 0, stream, residual, (const float*)x, ps, xs, first, n);
-  else if (dtype == TS_BF16) TS_LAUNCH("stream_add", stream_add_kernel<__nv_bfloat16>, num_rows, threads, 0, stream, residual, (const __nv_bfloat16*)x, ps, xs, first, n);
+  const int tiles = (n + threads - 1) / threads;
+  const dim3 grid(num_rows, num_rows >= 512 ? (tiles < 2 ? tiles : 2) : (tiles < 64 ? tiles : 64));
+  if (dtype == TS_F32) TS_LAUNCH("stream_add", stream_add_kernel<float>, grid, threads, 0, stream, residual, (const float*)x, ps, xs, first, n);
+  else if (dtype == TS_BF16) TS_LAUNCH("stream_add", stream_add_kernel<__nv_bfloat16>, grid, threads, 0, stream, residual, (const __nv_bfloat16*)x, ps, xs, first, n);
   else return ts_fail("stream_add: unknown dtype %d", dtype);
   return 0;
 }
