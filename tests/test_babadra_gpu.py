@@ -269,6 +269,10 @@ def test_latent_rows_turn_in_neighbouring_pairs_with_stretched_waves(dtype, tol,
     got = ops.gate_heads(values, None)
     want = torch.einsum("thr,hvr->thv", mixed[..., :r], w_uv.view(H, nv, r)).reshape(T, H * nv)
     assert (got.double().cpu() - want).abs().max() <= 2 * tol * want.abs().max()
+    straight = ops.batched_matmul(on_device(mixed, dtype)[:, :, :r].transpose(0, 1), on_device(w_uv, dtype).view(H, nv, r).transpose(1, 2),
+                                  side_by_side=True)
+    assert straight.shape == got.shape and straight.is_contiguous()
+    assert (straight.double() - got.double()).abs().max() <= tol * want.abs().max(), "the product writes the heads side by side itself"
 
 
 # ----------------------------------------------------------------------------- two score maps

@@ -1617,14 +1617,21 @@ def gate_heads(x, gate=None):
     return out
 
 
-def batched_matmul(a, b):
+def batched_matmul(a, b, side_by_side=False):
     """[B, M, N] = a [B, M, K] @ b [B, K, N], any strides, 32-bit sums.  bfloat16 operands go to the
     library's batched product (as the plain products of many rows do); float32 operands to this
-    package's FMA kernel."""
+    package's FMA kernel.  With ``side_by_side`` the result is [M, B * N]: every row's B results
+    laid side by side (the library's product writes them there itself)."""
     _cuda(a, b)
     B, M, K = a.shape
     if b.shape[0] != B or b.shape[1] != K or a.dtype != b.dtype:
         raise ValueError(f"batched_matmul: {tuple(a.shape)} does not fit {tuple(b.shape)}")
+    if side_by_side:
+        if a.dtype != torch.bfloat16:
+            return gate_heads(batched_matmul(a, b), None)
+        out = torch.empty(M, B, b.shape[2], dtype=a.dtype, device=a.device)
+        torch.bmm(a, b, out=out.transpose(0, 1))      # (leading dimension B * N, batches N apart)
+        return out.view(M, B * b.shape[2])
     if a.dtype == torch.bfloat16:
         return torch.bmm(a, b)
     N = b.shape[2]

@@ -116,9 +116,11 @@ class LatentAttention(Mixer):
         q_rows = ops.latent_query(carried, q, H, n, nr, self.stored_dim, self.position, ctx.positions)
         mixed = ops.paged_attention(q_rows, rows, rows, view, ctx, self.scale, sinks=self._sinks)
         # [H, T, kv_rank] x [H, kv_rank, vdim]: every head's weighted latent expanded to its values
-        values = ops.batched_matmul(mixed[:, :, :r].transpose(0, 1), self.w["v_up.weight"].view(H, nv, r).transpose(1, 2))
-        gate = proj[:, self.q_rank + self.kv_size:] if self.gate else None
-        return ops.linear(ops.gate_heads(values, gate), self.w["o_proj.weight"], allow_pending=True)
+        wide, w_uv = mixed[:, :, :r].transpose(0, 1), self.w["v_up.weight"].view(H, nv, r).transpose(1, 2)
+        if not self.gate:
+            return ops.linear(ops.batched_matmul(wide, w_uv, side_by_side=True), self.w["o_proj.weight"], allow_pending=True)
+        gate = proj[:, self.q_rank + self.kv_size:]
+        return ops.linear(ops.gate_heads(ops.batched_matmul(wide, w_uv), gate), self.w["o_proj.weight"], allow_pending=True)
 
 
 register_mixer("latent_attention", LatentAttention)
