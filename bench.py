@@ -787,8 +787,7 @@ def babadra_kernel_table(width, peaks):
     over one latent head (both designs: the same kernel, here without a sink); attention with two capped score
     maps per head (the attention kernel on twice the heads with the cap, then the maps' difference) beside
     Delilorn's window attention and plain attention of as many heads (prefill: FLOPs of the visible keys over the
-    library's GEMM rate; decode: bytes of the cached keys and values, the values once per key/value head, as
-    the design needs them); the experts with the bounded gate beside Delilorn's (prefill: FLOPs of the chosen
+    library's GEMM rate; decode: bytes of the cached keys and values, the values once per key/value head); the experts with the bounded gate beside Delilorn's (prefill: FLOPs of the chosen
     experts; decode: bytes of all experts' weights); the dense bounded feed-forward beside the gated one of
     Qwen3; the add of a sub-layer's output times its factors with the next norm beside Delilorn's norm + add +
     norm.  Decode launches are replayed from a graph, as the engine replays a decode step."""
@@ -821,9 +820,9 @@ def babadra_kernel_table(width, peaks):
             sc.host = {"cu_q": cu.tolist(), "kv_lens": [kv_len] * B}
             return sc
 
-        def attention(H, G, D, window=0, keep=0, sinks=None, shared=False, softcap=0.0, after=None):
+        def attention(H, G, D, window=0, keep=0, sinks=None, shared=False, softcap=0.0, after=None, value_heads=0):
             kc = torch.randn(B * pages_per + 1, G, page, D, device=dev).to(bf)
-            vc = kc if shared else torch.randn_like(kc)
+            vc = kc if shared else torch.randn(B * pages_per + 1, value_heads or G, page, D, device=dev).to(bf)
             view = GroupView(page, pages_per, None, table, kc.shape[0])
             q = torch.randn(T, H, D, device=dev).to(bf)
             sc = context()
@@ -849,9 +848,9 @@ def babadra_kernel_table(width, peaks):
              attention_roof(heads, D, 1, 0))
         H2, G2 = two["heads"], two["kv_heads"]
         combine = lambda o: ops.map_difference(o, H2, G2, 128, 0.8, 1e-6, 0.5)
-        frac(f"two_map_attention_{name}", attention(2 * H2, 2 * G2, 128, softcap=two["softcap"], after=combine),
+        frac(f"two_map_attention_{name}", attention(2 * H2, 2 * G2, 128, softcap=two["softcap"], after=combine, value_heads=G2),
              attention_roof(2 * H2, 128, 2 * G2, G2))
-        frac(f"two_map_attention_kernel_alone_{name}", attention(2 * H2, 2 * G2, 128, softcap=two["softcap"]),
+        frac(f"two_map_attention_kernel_alone_{name}", attention(2 * H2, 2 * G2, 128, softcap=two["softcap"], value_heads=G2),
              attention_roof(2 * H2, 128, 2 * G2, G2))
         frac(f"attention_as_many_heads_{name}", attention(2 * H2, 2 * G2, 128), attention_roof(2 * H2, 128, 2 * G2, 2 * G2))
         Gw = win["kv_heads"]
@@ -860,7 +859,7 @@ def babadra_kernel_table(width, peaks):
         # what stands before the attention kernel: norm of q and k per map, rotation, the maps' rows, keys and value copies
         qkv = torch.randn(T, (2 * H2 + 2 * G2) * 128 + G2 * 128, device=dev).to(bf)
         kc = torch.zeros(B * pages_per + 1, 2 * G2, page, 128, device=dev, dtype=bf)
-        vc = torch.zeros_like(kc)
+        vc = torch.zeros(B * pages_per + 1, G2, page, 128, device=dev, dtype=bf)
         slots = torch.cat([table[b, (s + torch.arange(m, device=dev)) // page] * page + (s + torch.arange(m, device=dev)) % page
                            for b, (s, m) in enumerate(zip(starts, lengths))]).int()
         positions = torch.cat([torch.arange(s, s + m) for s, m in zip(starts, lengths)]).int().to(dev)
@@ -872,7 +871,7 @@ def babadra_kernel_table(width, peaks):
         frac(f"two_map_norm_rotary_cache_write_{name}", timed(lambda: ops.rope_unit_kvwrite(
             qkv[:, :q_end], qkv[:, q_end:k_end], qkv[:, k_end:], positions, 2 * H2, 2 * G2, 128, 128, 128, rotary=rotary,
             k_cache=kc, v_cache=vc, slot_mapping=slots, page_size=page, q_weight=wq, k_weight=wq, pre_eps=1e-6, maps=2)),
-            T * ((2 * H2 + 2 * G2 + G2) * 128 * 2 + (2 * H2 + 4 * G2) * 128 * 2) / (peaks["hbm_gbs"] * 1e3))
+            T * (2 * H2 + 2 * G2 + G2) * 128 * 2 * 2 / (peaks["hbm_gbs"] * 1e3))
         # (the like kernel of Delilorn's window attention: as many heads, rotation and cache write alone)
         qkv1 = torch.randn(T, (heads + 2 * Gw) * 128, device=dev).to(bf)
         kc1 = torch.zeros(B * pages_per + 1, Gw, page, 128, device=dev, dtype=bf)

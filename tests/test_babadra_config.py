@@ -61,9 +61,9 @@ def test_run_order_caches_and_stream_operations():
     assert [c.cache for c in p.calls] == [0, 1, 2, 3, 4, 5] and all(c.writes_cache for c in p.calls)
     assert [len(c.before) for c in p.calls] == [0, 0, 0, 1, 0, 0]
     assert p.blocks[2].ffn is None and p.blocks[0].layer_scale and p.lm_head is not None and p.embed_position is not None
-    # two score maps: twice the key/value heads in the cache, rows as wide as the wider of key and value
+    # two score maps: a key head per map and one value head for both, rows as wide as the wider of key and value
     kinds = [(g.kind, [(t.name, t.heads, t.width) for t in g.tensors]) for g in p.cache_groups]
-    assert sorted(kinds) == [("full", [("k", 4, 32), ("v", 4, 32)]), ("full", [("latent", 1, 32)])]      # 24 + 8, and 20 + 12
+    assert sorted(kinds) == [("full", [("k", 4, 32), ("v", 2, 32)]), ("full", [("latent", 1, 32)])]      # 24 + 8, and 20 + 12
     assert p.group_sizes == [3, 3]
     q = build_model(babadra_config("Q"))
     assert [c.layer for c in q.calls] == [0, 1, 2, 3] and not q.stream_ops and q.spec.logit_softcap == 0.0

@@ -330,7 +330,7 @@ def test_two_score_maps_over_the_same_values(dtype, tol, H, G, n, nv, page, cap)
     D = -(-max(n, nv) // 16) * 16
     table, slots, pages = _pages(kv_lens, page, seed=2)
     kc = torch.full((pages, 2 * G, page, D), 30.0).to(dtype).to(DEV)
-    vc = torch.full((pages, 2 * G, page, D), 30.0).to(dtype).to(DEV)
+    vc = torch.full((pages, G, page, D), 30.0).to(dtype).to(DEV)            # one value head for both maps of a key/value head
     pos = torch.cat([torch.arange(kv) for kv in kv_lens]).to(torch.int32).to(DEV)
     x = on_device(h, dtype)
     q_end, k_end = 2 * H * n, 2 * (H + G) * n

@@ -58,6 +58,7 @@ struct MmaAttnParams {
   float* part_ml;           // [T, H, splits, 2]  (max in the log2 domain, sum)
   int cluster_merge;        // the key ranges of a (request, KV group) form a cluster and merge in shared memory
   int H, Hkv, page_shift, page_mask, max_blocks;
+  int v_share, Hv;          // `v_share` key heads in a row read one value head: the value cache holds Hv = Hkv / v_share heads
   int heads_per_tile, queries_per_tile, head_tiles;
   int num_splits, window;
   int keep_first;           // with a window: keys below this stay visible
@@ -131,13 +132,14 @@ __device__ __forceinline__ void load_kv_tile(char* ks, char* vs, const MmaAttnPa
     const int key = i / CH, c = i % CH;
     const int j = j0 + key;
     const bool valid = (j >= j_lo || j < keep) && j < j_hi;
-    size_t off = 0;
+    size_t off = 0, offv = 0;
     if (valid) {
       const size_t page = bt[j >> p.page_shift];
       off = (((page * p.Hkv + kvh) << p.page_shift) + (j & p.page_mask)) * D + c * 8;
+      offv = (((page * p.Hv + kvh / p.v_share) << p.page_shift) + (j & p.page_mask)) * D + c * 8;
     }
     cp_async16(smem_u32(ks + key * ROW_BYTES + c * 16), p.k_cache + off, valid);
-    cp_async16(smem_u32(vs + key * ROW_BYTES + c * 16), p.v_cache + off, valid);
+    cp_async16(smem_u32(vs + key * ROW_BYTES + c * 16), p.v_cache + offv, valid);
   }
 }
 
@@ -578,7 +580,7 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
           const int values = i & 1, c = (i >> 1) % (D / 64), pg = (i >> 1) / (D / 64);
           const int j = tile * BN + (pg << p.page_shift);
           const int page = j < j_hi ? bt[j >> p.page_shift] : 0;                        // past the end: the null page
-          const int row = (page * p.Hkv + kvh) << p.page_shift;
+          const int row = (values ? page * p.Hv + kvh / p.v_share : page * p.Hkv + kvh) << p.page_shift;
           const int off = stage * KV_TILE + c * (BN * 128) + (pg << p.page_shift) * 128;
           tma_load_2d(smem_u32((values ? Vs : Ks) + off), values ? map_v : map_k, bar, c * 64, row);
         }
@@ -880,7 +882,8 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
                              int num_tokens, int num_requests, int max_q_len, int H, int Hkv, int page_size,
                              int max_blocks, float scale, int window, int num_splits, float* part_o,
                              float* part_ml, int decode_only, const int* tile_req,
-                             const int* tile_q0, int num_tiles, int tile_queries, int num_pages, cudaStream_t stream);
+                             const int* tile_q0, int num_tiles, int tile_queries, int num_pages, int v_share,
+                             cudaStream_t stream);
 }
 
 TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cache, const void* v_cache,
@@ -890,7 +893,7 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
                                      int num_splits, float* part_o, float* part_ml,
                                      int decode_only, const int* tile_req, const int* tile_q0, int num_tiles,
                                      int tile_queries, int num_pages, int keep_first, const float* sinks,
-                                     int chunk, const float* slopes, float softcap, cudaStream_t stream) {
+                                     int chunk, const float* slopes, float softcap, int v_share, cudaStream_t stream) {
   TS_REQUIRE(keep_first >= 0, "paged_attention_mma: keep_first %d", keep_first);
   TS_REQUIRE(chunk >= 0 && (chunk == 0 || window <= 0), "paged_attention_mma: a chunk of %d positions (and no window beside it)", chunk);
   MmaAttnParams extra = {};
@@ -902,7 +905,7 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
   return paged_attention_mma_impl(&extra, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
                                   num_requests, max_q_len, H, Hkv, page_size, max_blocks, scale, window, num_splits,
                                   part_o, part_ml, decode_only, tile_req, tile_q0, num_tiles,
-                                  tile_queries, num_pages, stream);
+                                  tile_queries, num_pages, v_share, stream);
 }
 
 // Decode (every request brings one token) straight from the fused q/k/v projection: qkv
@@ -940,7 +943,7 @@ TS_EXPORT int ts_paged_attention_mma_from_qkv(const void* qkv, const float* part
   extra.k_cache_out = static_cast<bf16*>(k_cache); extra.v_cache_out = static_cast<bf16*>(v_cache);
   return paged_attention_mma_impl(&extra, nullptr, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
                                   num_requests, 1, H, Hkv, page_size, max_blocks, scale, window, num_splits, part_o,
-                                  part_ml, merge, nullptr, nullptr, 0, 0, num_pages, stream);
+                                  part_ml, merge, nullptr, nullptr, 0, 0, num_pages, 1, stream);
 }
 
 namespace {
@@ -949,8 +952,10 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
                              int num_tokens, int num_requests, int max_q_len, int H, int Hkv, int page_size,
                              int max_blocks, float scale, int window, int num_splits, float* part_o,
                              float* part_ml, int decode_only, const int* tile_req,
-                             const int* tile_q0, int num_tiles, int tile_queries, int num_pages, cudaStream_t stream) {
+                             const int* tile_q0, int num_tiles, int tile_queries, int num_pages, int v_share,
+                             cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_mma: empty batch");
+  TS_REQUIRE(v_share >= 1 && Hkv % v_share == 0, "paged_attention_mma: %d key heads do not share values in runs of %d", Hkv, v_share);
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_mma: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size > 0 && (page_size & (page_size - 1)) == 0, "paged_attention_mma: page size %d is no power of two", page_size);
   TS_REQUIRE(num_splits >= 1 && num_splits <= 64, "paged_attention_mma: num_splits %d out of range", num_splits);
@@ -966,6 +971,7 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
   TS_REQUIRE((tile_req == nullptr) == (tile_q0 == nullptr) && (tile_req == nullptr || num_tiles > 0),
              "paged_attention_mma: the work list is incomplete");
   p.H = H; p.Hkv = Hkv; p.max_blocks = max_blocks;
+  p.v_share = v_share; p.Hv = Hkv / v_share;
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.page_mask = page_size - 1;
@@ -983,12 +989,13 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
     if (tma) {
       EncodeTiledFn fn = encode_tiled();
       TS_REQUIRE(fn != nullptr, "paged_attention_mma: the driver's tensor-map encoder was not found");
-      const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * Hkv * page_size};
+      const cuuint64_t dims_k[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * Hkv * page_size};
+      const cuuint64_t dims_v[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * (Hkv / v_share) * page_size};
       const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
       const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
       const cuuint32_t elem[2] = {1, 1};
       for (int i = 0; i < 2; ++i)
-        TS_REQUIRE(fn(i ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(i ? v_cache : k_cache), dims,
+        TS_REQUIRE(fn(i ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(i ? v_cache : k_cache), i ? dims_v : dims_k,
                       strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
                    "paged_attention_mma: cuTensorMapEncodeTiled failed for the cache");

@@ -44,6 +44,7 @@ struct AttnParams {
   float* part_o;            // [T, H, splits, D] (num_splits > 1)
   float* part_ml;           // [T, H, splits, 2]
   int H, Hkv, page_size, max_blocks;
+  int v_share, Hv;          // `v_share` key heads in a row read one value head: the value cache holds Hv = Hkv / v_share heads
   int heads_per_tile, queries_per_tile, head_tiles;
   int num_splits, window;
   int keep_first;           // with a window: keys below this stay visible
@@ -146,8 +147,9 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(AttnParams 
       if ((j >= j_lo || j < keep) && j < j_hi) {
         const size_t page = bt[j / p.page_size];
         const size_t off = ((page * p.Hkv + kvh) * p.page_size + j % p.page_size) * D + c;
+        const size_t offv = ((page * p.Hv + kvh / p.v_share) * p.page_size + j % p.page_size) * D + c;
         load_row_chunk<T>(kc + off, kv);
-        load_row_chunk<T>(vc + off, vv);
+        load_row_chunk<T>(vc + offv, vv);
       } else {
 #pragma unroll
         for (int e = 0; e < VN; ++e) kv[e] = vv[e] = 0.f;
@@ -275,14 +277,16 @@ TS_EXPORT int ts_attention_head_dim() { return D; }
 // Scratch for num_splits > 1: part_o holds T*H*splits*D floats, part_ml T*H*splits*2.
 // `chunk` > 0: queries see the keys of their own chunk of that many positions only (counted from
 // position 0; no window then).  `slopes` [H]: slopes[h] * (i - j) is taken off head h's scores.
+// `v_share` s >= 1: v_cache holds Hkv / s heads, and key head g reads value head g / s.
 TS_EXPORT int ts_paged_attention_biased(int dtype, const void* q, void* out, const void* k_cache,
                                         const void* v_cache, const int* block_table, const int* cu_q,
                                         const int* kv_lens, int num_tokens, int num_requests,
                                         int max_q_len, int H, int Hkv, int page_size, int max_blocks,
                                         float scale, int window, int num_splits, float* part_o,
                                         float* part_ml, int keep_first, const float* sinks, int chunk,
-                                        const float* slopes, float softcap, cudaStream_t stream) {
+                                        const float* slopes, float softcap, int v_share, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention: empty batch");
+  TS_REQUIRE(v_share >= 1 && Hkv % v_share == 0, "paged_attention: %d key heads do not share values in runs of %d", Hkv, v_share);
   TS_REQUIRE(chunk >= 0 && (chunk == 0 || window <= 0), "paged_attention: a chunk of %d positions (and no window beside it)", chunk);
   TS_REQUIRE(keep_first >= 0, "paged_attention: keep_first %d", keep_first);
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention: %d heads over %d KV heads", H, Hkv);
@@ -295,6 +299,7 @@ TS_EXPORT int ts_paged_attention_biased(int dtype, const void* q, void* out, con
   p.block_table = block_table; p.cu_q = cu_q; p.kv_lens = kv_lens;
   p.part_o = part_o; p.part_ml = part_ml;
   p.H = H; p.Hkv = Hkv; p.page_size = page_size; p.max_blocks = max_blocks;
+  p.v_share = v_share; p.Hv = Hkv / v_share;
   const int G = H / Hkv;
   p.heads_per_tile = G < BM ? G : BM;
   p.queries_per_tile = G < BM ? BM / G : 1;
@@ -335,7 +340,7 @@ TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void
                                  float* part_ml, int keep_first, const float* sinks, cudaStream_t stream) {
   return ts_paged_attention_biased(dtype, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens, num_requests,
                                    max_q_len, H, Hkv, page_size, max_blocks, scale, window, num_splits, part_o, part_ml,
-                                   keep_first, sinks, 0, nullptr, 0.f, stream);
+                                   keep_first, sinks, 0, nullptr, 0.f, 1, stream);
 }
 
 // ------------------------------------------------------------------ no-allocation entry point

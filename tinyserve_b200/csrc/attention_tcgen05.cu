@@ -71,6 +71,7 @@ struct TcAttnParams {
   const int* tile_req;      // optional work list: request and first query of every block
   const int* tile_q0;
   int H, Hkv, page_shift, page_size, max_blocks;
+  int v_share, Hv;          // `v_share` key heads in a row read one value head: the value cache holds Hv = Hkv / v_share heads
   int heads_per_tile, queries_per_tile, head_tiles;     // of one query tile
   int window;
   int keep_first;           // with a window: keys below this stay visible (their tiles come first in the walk)
@@ -211,7 +212,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const int pg = i / DCH, c = i % DCH;
           const int j = j0 + (pg << p.page_shift);
           const int page = j < j_hi ? bt[j >> p.page_shift] : 0;          // past the end: the null page
-          const int row = (page * p.Hkv + kvh) << p.page_shift;
+          const int row = (keys ? page * p.Hkv + kvh : page * p.Hv + kvh / p.v_share) << p.page_shift;
           const int off = s * KV_BYTES + c * CHUNK_BYTES + (pg << p.page_shift) * 128;
           if (keys) tma_load_2d(smem_u32(Ks + off), &map_k, bar, c * 64, row);
           else tma_load_2d(smem_u32(Vs + off), &map_v, bar, c * 64, row);
@@ -524,8 +525,9 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
                                          int num_pages, int page_size, int max_blocks, float scale, int window,
                                          const int* tile_req, const int* tile_q0, int num_tiles,
                                          int tile_queries, int keep_first, const float* sinks, int chunk,
-                                         const float* slopes, float softcap, cudaStream_t stream) {
+                                         const float* slopes, float softcap, int v_share, cudaStream_t stream) {
   TS_REQUIRE(keep_first >= 0, "paged_attention_tcgen05: keep_first %d", keep_first);
+  TS_REQUIRE(v_share >= 1 && Hkv % v_share == 0, "paged_attention_tcgen05: %d key heads do not share values in runs of %d", Hkv, v_share);
   TS_REQUIRE(chunk >= 0 && (chunk == 0 || window <= 0), "paged_attention_tcgen05: a chunk of %d positions (and no window beside it)", chunk);
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_tcgen05: empty batch");
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_tcgen05: %d heads over %d KV heads", H, Hkv);
@@ -539,6 +541,7 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
   p.out = (bf16*)out; p.block_table = block_table; p.cu_q = cu_q; p.kv_lens = kv_lens;
   p.tile_req = tile_req; p.tile_q0 = tile_q0;
   p.H = H; p.Hkv = Hkv; p.page_size = page_size; p.max_blocks = max_blocks; p.window = window;
+  p.v_share = v_share; p.Hv = Hkv / v_share;
   p.keep_first = keep_first; p.sinks = sinks;
   p.chunk = chunk; p.slopes = slopes;
   p.page_shift = 0;
@@ -561,10 +564,11 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
   }
   {
     const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * Hkv * page_size};
+    const cuuint64_t dims_v[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * (Hkv / v_share) * page_size};
     const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
     const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
     TS_REQUIRE(encode(&mk, const_cast<void*>(k_cache), 2, dims, strides, box), "paged_attention_tcgen05: tensor map of the keys failed");
-    TS_REQUIRE(encode(&mv, const_cast<void*>(v_cache), 2, dims, strides, box), "paged_attention_tcgen05: tensor map of the values failed");
+    TS_REQUIRE(encode(&mv, const_cast<void*>(v_cache), 2, dims_v, strides, box), "paged_attention_tcgen05: tensor map of the values failed");
   }
   static bool configured = false;
   if (!configured) {

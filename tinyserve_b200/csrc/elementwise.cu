@@ -1390,7 +1390,8 @@ TS_EXPORT int ts_mean_of_normed(int dtype, int count, const void* const* xs, con
 // heads.  The attention kernels see H query heads on G key/value heads; since they give query
 // head i the key/value head i / (H / G), a head's maps are stored apart: map m of head h, which
 // belongs to kv head g = h / r (r heads per kv head), goes to query row g M r + m r + h % r, which
-// is served by key/value head g M + m: the key of (g, m) beside a copy of the value of g.
+// is served by key head g M + m; the value cache holds G / M heads, and the attention kernels give
+// key head i the value head i / M (their `v_share`).
 template <typename T>
 __global__ void rope_unit_kvwrite_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, long long ldk,
                                          const T* __restrict__ v, long long ldv, T* __restrict__ q_out,
@@ -1422,12 +1423,10 @@ __global__ void rope_unit_kvwrite_kernel(const T* __restrict__ q, long long ldq,
       const int g = is_v ? head - H - G : head - H;
       const size_t page = slot / page_size, in_page = slot % page_size;
       if (is_v) {
-        // the value head, once for every map's key/value head
+        // the value cache holds G / maps heads: the maps of a key/value head read the same one
         src = v + (size_t)t * ldv + (size_t)g * vdim;
-        for (int m = 0; m < maps; ++m) {
-          dst = v_cache + ((page * G + g * maps + m) * page_size + in_page) * D;
-          for (int i = lane; i < D; i += 32) dst[i] = i < vdim ? src[i] : from_f32<T>(0.f);
-        }
+        dst = v_cache + ((page * (G / maps) + g) * page_size + in_page) * D;
+        for (int i = lane; i < D; i += 32) dst[i] = i < vdim ? src[i] : from_f32<T>(0.f);
         continue;
       }
       src = k + (size_t)t * ldk + (size_t)g * dim;

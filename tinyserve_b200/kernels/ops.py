@@ -871,7 +871,7 @@ def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work, kee
         c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale), c_int(window),
         c_int(num_splits), _ptr(part_o), _ptr(part_ml), c_int(2 if cluster else 1), _ptr(work.dec_req),
         _ptr(work.dec_tok), c_int(n), c_int(0), c_int(_tma_pages(k_cache, v_cache)), c_int(keep_first), _ptr(sinks),
-        c_int(chunk), _ptr(slopes), c_float(softcap), _stream()),
+        c_int(chunk), _ptr(slopes), c_float(softcap), c_int(Hkv // v_cache.shape[1]), _stream()),
         2 if num_splits > 1 and not cluster else 1)
 
 
@@ -915,6 +915,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
     ``keep_first`` (with a window): the first keys of a sequence stay visible to every later query.
     ``sinks`` float32 [H]: head h's softmax sum holds one more term exp(sinks[h]) without key or value.
     ``softcap`` c > 0: the scaled score s becomes c tanh(s / c) (before the slopes' bias).
+    A value cache of fewer heads than the key cache (Hkv / s): key head i reads value head i / s.
     q [T, H, D]; caches [pages, Hkv, page_size, D]; ``view`` a GroupView; ``ctx`` gives cu_q,
     kv_lens and the batch's maxima.  bfloat16 runs on the tensor cores (a decode kernel when
     every request brings one token, else a prefill kernel); float32 on the 32-bit kernel.
@@ -922,6 +923,9 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
     _cuda(q, k_cache, v_cache)
     T, H, D = q.shape
     Hkv = k_cache.shape[1]
+    if Hkv % v_cache.shape[1]:
+        raise ValueError(f"paged_attention: {Hkv} key heads on {v_cache.shape[1]} value heads")
+    v_share = Hkv // v_cache.shape[1]          # key head i reads value head i / v_share
     page = view.page_size
     chosen = attention_backend(q.dtype, D, page)
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.shape != (H,) or not sinks.is_cuda):
@@ -957,7 +961,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
                 c_int(k_cache.shape[0]), c_int(page), c_int(view.block_table.stride(0)), c_float(scale),
                 c_int(window), _ptr(work.tile_req), _ptr(work.tile_q0), c_int(work.num_tiles),
                 c_int(tile_queries), c_int(keep_first), _ptr(sinks), c_int(chunk), _ptr(slopes), c_float(softcap),
-                _stream()))
+                c_int(v_share), _stream()))
         return out
     if num_splits is None:
         if decode:
@@ -996,7 +1000,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml),
             c_int((2 if cluster else 1) if decode else 0), _ptr(tile_req), _ptr(tile_q0), c_int(num_tiles), c_int(tile_queries),
             c_int(_tma_pages(k_cache, v_cache)), c_int(keep_first), _ptr(sinks), c_int(chunk), _ptr(slopes),
-            c_float(softcap), _stream()),
+            c_float(softcap), c_int(v_share), _stream()),
             launches)
         return out
     lib = _attention(D)
@@ -1005,7 +1009,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         _ptr(ctx.cu_q), _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len),
         c_int(H), c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)),
         c_float(scale), c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), c_int(keep_first),
-        _ptr(sinks), c_int(chunk), _ptr(slopes), c_float(softcap), _stream()),
+        _ptr(sinks), c_int(chunk), _ptr(slopes), c_float(softcap), c_int(v_share), _stream()),
         launches)
     return out
 
@@ -1334,9 +1338,10 @@ def rope_unit_kvwrite(q, k, v, positions, num_heads, num_kv_heads, dim, vdim, st
     ``q_weight`` / ``k_weight`` ([dim] each): every head of q and k is RMS-normed with that weight
     (``pre_eps``) before the rotation.  ``maps`` M > 1: every head has M score maps over the same
     values; ``num_heads`` and ``num_kv_heads`` then count (head, map) pairs, laid out head by head
-    in q and k, v holds ``num_kv_heads`` / M heads, and the returned query rows and the cache heads
-    are arranged so that the attention kernels pair map m of a head with map m of its key/value
-    head and a copy of that head's value (``map_difference`` reads the output in that order)."""
+    in q and k, v holds ``num_kv_heads`` / M heads and so does the value cache, and the returned
+    query rows are arranged so that the attention kernels pair map m of a head with map m of its
+    key/value head (``paged_attention`` gives key head i the value head i / M; ``map_difference``
+    reads the output in that order)."""
     _cuda(q, k, v, positions, k_cache, v_cache, slot_mapping, q_weight, k_weight)
     T = q.shape[0]
     if maps < 1 or num_heads % maps or num_kv_heads % maps:
@@ -1347,7 +1352,8 @@ def rope_unit_kvwrite(q, k, v, positions, num_heads, num_kv_heads, dim, vdim, st
             q_weight.dtype != k_weight.dtype or q_weight.shape != (dim,) or k_weight.shape != (dim,))):
         raise TypeError("rope_unit_kvwrite: q and k norm weights come together, [dim] each and alike in dtype")
     if k_cache is not None and (k_cache.dtype != q.dtype or k_cache.shape[-1] != stored_dim or not k_cache.is_contiguous()
-                                or not v_cache.is_contiguous()):
+                                or not v_cache.is_contiguous() or k_cache.shape[1] != num_kv_heads
+                                or v_cache.shape[1] != num_kv_heads // maps):
         raise TypeError("rope_unit_kvwrite: the cache does not fit the activations")
     out = torch.empty(T, num_heads, stored_dim, dtype=q.dtype, device=q.device)
     cos = rotary.cos if rotary is not None else None

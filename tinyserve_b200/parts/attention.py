@@ -35,8 +35,8 @@ holds 2 dim columns per head and k 2 dim per key/value head, [map 1 | map 2]; ea
 head's values; with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + d (four learned vectors of dim
 elements, one number per layer, made once in 32-bit) the head's output is
 o = a_1 - lambda a_2, divided by sqrt(mean(o^2) + e) over its value columns and multiplied by 1 - d.
-The attention kernels run it as 2 H query heads on 2 G key/value heads (the value of a key/value
-head is kept beside both of its maps' keys); ``ops.map_difference`` then combines the pairs."""
+The attention kernels run it as 2 H query heads on 2 G key heads that read G value heads (key
+head i reads value head i / 2); ``ops.map_difference`` then combines the pairs."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -169,7 +169,13 @@ class Attention(Mixer):
 
     def cache_spec(self):
         kind = "window" if self.window > 0 else "full"
-        return CacheSpec(kind, self.num_kv_heads * self.maps, self.stored_dim, self.window, keep_first=self.keep_first)
+        if self.maps > 1:
+            # a key head per map, one value head for both
+            from .base import CacheTensor
+            tensors = (CacheTensor("k", self.num_kv_heads * self.maps, self.stored_dim), CacheTensor("v", self.num_kv_heads, self.stored_dim))
+            return CacheSpec(kind, self.num_kv_heads * self.maps, self.stored_dim, self.window, tensors=tensors,
+                             keep_first=self.keep_first)
+        return CacheSpec(kind, self.num_kv_heads, self.stored_dim, self.window, keep_first=self.keep_first)
 
     def _biased(self):
         return self.chunk > 0 or self.slope_values is not None
