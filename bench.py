@@ -856,7 +856,7 @@ def babadra_kernel_table(width, peaks):
         Gw = win["kv_heads"]
         frac(f"delilorn_window_attention_{name}", attention(heads, Gw, 128, win["mask"]["size"], win["mask"]["keep_first"]),
              attention_roof(heads, 128, Gw, Gw, win["mask"]["size"], win["mask"]["keep_first"]))
-        # what stands before the attention kernel: norm of q and k per map, rotation, the maps' rows, keys and value copies
+        # what stands before the attention kernel: norm of q and k per map, rotation, the maps' rows, keys and values
         qkv = torch.randn(T, (2 * H2 + 2 * G2) * 128 + G2 * 128, device=dev).to(bf)
         kc = torch.zeros(B * pages_per + 1, 2 * G2, page, 128, device=dev, dtype=bf)
         vc = torch.zeros(B * pages_per + 1, G2, page, 128, device=dev, dtype=bf)

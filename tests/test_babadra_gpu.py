@@ -316,8 +316,8 @@ def _two_map_case(H, G, n, nv, rot, scale, cap, diff, kv_lens, seed):
                                            (4, 1, 64, 64, 32), (2, 1, 128, 128, 64), (2, 2, 32, 128, 16)])
 @pytest.mark.parametrize("cap", [None, 3.0, 40.0])
 def test_two_score_maps_over_the_same_values(dtype, tol, H, G, n, nv, page, cap):
-    """q/k norm with shared weights, rotation of a part of every map, the maps' rows and the copies of
-    the values as the attention kernels want them, capped scores, the maps' difference normed per head:
+    """q/k norm with shared weights, rotation of a part of every map, the maps' rows as the
+    attention kernels want them, one value head for both maps, capped scores, the maps' difference normed per head:
     a whole prompt, single tokens, a portion after a prefix, two tokens and a request of one token, on
     every attention kernel that takes the head size, with and without key ranges."""
     from tinyserve_b200.kernels import ops
